@@ -1,0 +1,134 @@
+/* ozb.h -- C ABI of libozaki_blackwell.so, the B200 (sm_100a) build of the Ozaki scheme II matrix products.
+ *
+ * The first eight functions are the reference's C ABI, symbol for symbol (reference file python/capi.cu, lines cited at
+ * each declaration): same names, argument order, meaning and error convention, so that the reference's ctypes wrapper
+ * (python/ozaki_blackwell/__init__.py:26-36) binds to this library unchanged. All matrices are row-major float64,
+ * A is M x K, B is K x N, C is M x N. Every function returns 0 or an error code (a cudaError_t value or one of the
+ * OZB_E* codes below); ozb_error() turns a code into text. Nothing aborts the process or throws across this boundary.
+ * Calls are serialised by one process-wide mutex, as in the reference (python/capi.cu:19).
+ *
+ * The functions after them are additions with the same conventions: leading dimensions and streams, the plan-level
+ * interface that C++ callers of the reference get from src/ozaki2.cuh (oz::plan / oz::dgemm / oz::release), and the
+ * four stages as separate calls, which the reference's phase benchmark launches directly (bench/phases.cu:21-30).
+ */
+#ifndef OZB_H
+#define OZB_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    OZB_EARG = 10001,     /* python/capi.cu:17 -- M, N, K not positive, or moduli outside 8..16 */
+    OZB_EK = 10002,       /* python/capi.cu:17 -- K >= 131072: the int32 accumulators of the INT8 GEMMs would overflow */
+    OZB_EARCH = 10003,    /* python/capi.cu:17 -- unsupported GPU; here: anything that is not compute capability 10.x */
+    OZB_ETIMEOUT = 10004, /* addition: a bounded wait inside the GEMM kernel expired; the result is not valid */
+    OZB_ENOTBUILT = 10005,/* addition: the entry point exists for ABI compatibility but this build has no kernel for it */
+    OZB_ESIZE = 10006     /* addition: a size exceeds a stated fixed limit of the entry point */
+};
+
+/* ---- the reference's ABI ------------------------------------------------------------------------------------- */
+
+/* python/capi.cu:52 -- version string of the library */
+const char *ozb_version(void);
+
+/* python/capi.cu:54-62 -- text for a return code (0 -> "ok") */
+const char *ozb_error(int code);
+
+/* python/capi.cu:65-74 -- current device: name (NUL-terminated, truncated to len), 10*major+minor, L2 size in KiB,
+ * SM count. Any of the out pointers may be NULL. */
+int ozb_device(char *name, int len, int *sm, int *l2_kib, int *sms);
+
+/* python/capi.cu:77-89 -- C = A B in FP64 with `moduli` moduli (8..16). on_host = 0: A, B, C are device pointers valid
+ * on the current device; on_host = 1: host pointers, staged by the library. Synchronous: returns after the device is
+ * idle. Dense operands (lda = K, ldb = N, ldc = N). */
+int ozb_dgemm(int M, int N, int K, const double *A, const double *B, double *C, int moduli, int on_host);
+
+/* python/capi.cu:92-105 -- (Ch + Cl) = (Ah + Al)(Bh + Bl) in double-double, 32 moduli. */
+int ozb_ddgemm(int M, int N, int K, const double *Ah, const double *Al, const double *Bh, const double *Bl, double *Ch,
+               double *Cl, int on_host);
+
+/* python/capi.cu:108-121 -- triple-double product, 49 moduli. Exported for ABI compatibility; this build returns
+ * OZB_ENOTBUILT after the argument checks. */
+int ozb_tdgemm(int M, int N, int K, const double *A0, const double *A1, const double *A2, const double *B0,
+               const double *B1, const double *B2, double *C0, double *C1, double *C2, int on_host);
+
+/* python/capi.cu:124-127 -- free the cached plans (device memory); the next call plans again */
+void ozb_release(void);
+
+/* python/capi.cu:130-164 -- GPU time of `reps` (1..101) products of fixed pseudo-random n x n matrices resident on the
+ * device, through the public entry point; the median in ms. kind 0 FP64 (16 moduli), 1 double-double, 2 triple-double. */
+int ozb_bench(int n, int kind, int reps, double *median_ms);
+
+/* ---- additions ----------------------------------------------------------------------------------------------- */
+
+/* src/ozaki2.cuh:101-108 (oz::bits_for) -- scaling bits for nm moduli at inner dimension K; -1 if K >= 131072 */
+int ozb_bits_for(int nm, int K, int maxbits);
+/* src/ozaki2.cuh:24-34 (oz::modulus) -- the l-th modulus, 0 <= l < 49 (0 otherwise) */
+int ozb_modulus(int l);
+
+/* The reference's oz::Plan (src/ozaki2.cuh:116-132) as an opaque handle: workspaces for one (M, N, K, moduli) shape on
+ * the device that is current at creation. */
+typedef struct ozb_plan ozb_plan;
+/* src/ozaki2.cuh:122-131 (oz::plan) */
+int ozb_plan_create(int M, int N, int K, int moduli, int maxbits, ozb_plan **out);
+/* src/ozaki2.cuh:132 (oz::release) */
+void ozb_plan_destroy(ozb_plan *p);
+/* src/ozaki2.cuh:134-164 (oz::dgemm) with leading dimensions (in elements) and a stream (a cudaStream_t passed as
+ * void*; NULL = the legacy default stream, which the reference uses). Asynchronous: it only enqueues work. */
+int ozb_plan_dgemm(ozb_plan *p, const double *A, long long lda, const double *B, long long ldb, double *C, long long ldc,
+                   void *stream);
+/* Split form for callers that stream B in column panels (multi-GPU row-block sharding, host staging): residues of A
+ * once, then any number of column panels [j0, j0 + ncols) of B and C; j0 must be a multiple of 256. B and C point at
+ * the panel's first column. */
+int ozb_plan_set_a(ozb_plan *p, const double *A, long long lda, void *stream);
+int ozb_plan_panel(ozb_plan *p, const double *B, long long ldb, double *C, long long ldc, int j0, int ncols, void *stream);
+/* Workspace view, for stage-by-stage checks against the reference's Plan fields (src/ozaki2.cuh:117-119):
+ * Ar [nm][M][Kp] int8, Br [nm][N][Kp] int8, Cr [nm][M][Np] int8 (balanced residues of the products, where the
+ * reference keeps int32 Cl), sa [M], sb [N]. */
+int ozb_plan_view(ozb_plan *p, int *bits, int *Kp, int *Np, int8_t **Ar, int8_t **Br, int8_t **Cr, int **sa, int **sb);
+/* Device status word of the plan: 0, or OZB_ETIMEOUT if a bounded wait expired in a kernel launched through it.
+ * Synchronises the stream the last call used. */
+int ozb_plan_status(ozb_plan *p);
+/* Milliseconds of the last ozb_plan_dgemm when the environment variable OZ_PROF is set (src/ozaki2.cuh:135-153):
+ * ms[0] scales + residues, ms[1] INT8 GEMMs, ms[2] CRT. Returns OZB_EARG when profiling is off. */
+int ozb_plan_phase_ms(ozb_plan *p, float ms[3]);
+
+/* ozb_dgemm with leading dimensions, on device pointers, on a stream, without the final synchronisation. Uses the same
+ * cached plan as ozb_dgemm. */
+int ozb_dgemm_ex(int M, int N, int K, const double *A, long long lda, const double *B, long long ldb, double *C,
+                 long long ldc, int moduli, void *stream);
+
+/* The four stages on caller-owned device buffers (what bench/phases.cu launches one by one). Asynchronous.
+ * Pitches: ld of int8 planes in bytes and a multiple of 16; `plane` = distance between planes in elements. */
+/* src/ozaki2.cuh:56-78 -- scales + residues of an A-like operand (rows of `len` contiguous doubles, pitch ldx) */
+int ozb_scale_residues_rows(int moduli, const double *X, int rows, int len, long long ldx, int bits, int *s, int8_t *R,
+                            int ld, size_t plane, void *stream);
+/* src/ozaki2.cuh:56-78 -- the same for a B-like operand (row-major rows x cols, scaled per column, written transposed
+ * as R[l][col][row]); colmax is scratch of `cols` 64-bit words */
+int ozb_scale_residues_cols(int moduli, const double *X, int rows, int cols, long long ldx, int bits, void *colmax, int *s,
+                            int8_t *R, int ld, size_t plane, void *stream);
+/* src/gemm_i8.cuh:148-160 (oz::gemm_i8_run) -- C[z] = A[z] Bt[z]^T, Z planes, int32 out [Z][M][ldc]. No padding
+ * requirement on M, N, K; lda/ldb in bytes, multiples of 16, base pointers 16-byte aligned. */
+int ozb_gemm_i8(const int8_t *A, const int8_t *Bt, int32_t *C, int M, int N, int K, int Z, long long lda, long long ldb,
+                long long ldc, size_t plane_a, size_t plane_b, size_t plane_c, void *stream);
+/* The same with the reduction of src/ozaki2.cuh:88 fused in: plane z comes out as int8 balanced residues mod
+ * ozb_modulus(first_modulus + z); ldc a multiple of 16 */
+int ozb_gemm_i8_mod(const int8_t *A, const int8_t *Bt, int8_t *C, int M, int N, int K, int Z, long long lda, long long ldb,
+                    long long ldc, size_t plane_a, size_t plane_b, size_t plane_c, int first_modulus, void *stream);
+/* src/ozaki2.cuh:82-97 (oz::crt) -- from int32 planes of raw products (the reference's layout) */
+int ozb_crt_i32(int moduli, const int32_t *Cl, size_t plane, int M, int N, long long ldr, const int *sa, const int *sb,
+                double *C, long long ldc, void *stream);
+/* the same from int8 planes of balanced residues (ldr a multiple of 4) */
+int ozb_crt_i8(int moduli, const int8_t *Cr, size_t plane, int M, int N, long long ldr, const int *sa, const int *sb,
+               double *C, long long ldc, void *stream);
+/* Status of the stage calls above (they share one device status word per device): 0 or OZB_ETIMEOUT. Synchronises
+ * the device. */
+int ozb_status(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OZB_H */

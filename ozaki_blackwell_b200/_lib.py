@@ -1,0 +1,61 @@
+"""ctypes binding of libozaki_blackwell.so (the C ABI declared in include/ozb.h).
+
+The library holds sm_100a code only and has no CPU path: importing this module builds nothing and computes nothing;
+it fails loudly if the shared library is missing (run `make -C ozaki_blackwell_b200/csrc` or __graft_entry__.build()).
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libozaki_blackwell.so")
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(f"{LIB_PATH} is missing: build it with `make -C {os.path.join(_HERE, 'csrc')}`; there is no fallback path")
+
+lib = ctypes.CDLL(LIB_PATH)
+
+_i, _ll, _p, _sz = ctypes.c_int, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_size_t
+_ip = ctypes.POINTER(ctypes.c_int)
+
+# the reference's eight (python/ozaki_blackwell/__init__.py:26-36 of the reference sets the same argtypes)
+lib.ozb_version.restype = ctypes.c_char_p
+lib.ozb_version.argtypes = []
+lib.ozb_error.restype = ctypes.c_char_p
+lib.ozb_error.argtypes = [_i]
+lib.ozb_device.argtypes = [ctypes.c_char_p, _i, _ip, _ip, _ip]
+lib.ozb_dgemm.argtypes = [_i] * 3 + [_p] * 3 + [_i] * 2
+lib.ozb_ddgemm.argtypes = [_i] * 3 + [_p] * 6 + [_i]
+lib.ozb_tdgemm.argtypes = [_i] * 3 + [_p] * 9 + [_i]
+lib.ozb_release.restype = None
+lib.ozb_release.argtypes = []
+lib.ozb_bench.argtypes = [_i] * 3 + [ctypes.POINTER(ctypes.c_double)]
+
+# additions
+lib.ozb_bits_for.argtypes = [_i, _i, _i]
+lib.ozb_modulus.argtypes = [_i]
+lib.ozb_plan_create.argtypes = [_i, _i, _i, _i, _i, ctypes.POINTER(_p)]
+lib.ozb_plan_destroy.restype = None
+lib.ozb_plan_destroy.argtypes = [_p]
+lib.ozb_plan_dgemm.argtypes = [_p, _p, _ll, _p, _ll, _p, _ll, _p]
+lib.ozb_plan_set_a.argtypes = [_p, _p, _ll, _p]
+lib.ozb_plan_panel.argtypes = [_p, _p, _ll, _p, _ll, _i, _i, _p]
+lib.ozb_plan_view.argtypes = [_p, _ip, _ip, _ip] + [ctypes.POINTER(_p)] * 5
+lib.ozb_plan_status.argtypes = [_p]
+lib.ozb_plan_phase_ms.argtypes = [_p, ctypes.POINTER(ctypes.c_float * 3)]
+lib.ozb_dgemm_ex.argtypes = [_i, _i, _i, _p, _ll, _p, _ll, _p, _ll, _i, _p]
+lib.ozb_scale_residues_rows.argtypes = [_i, _p, _i, _i, _ll, _i, _p, _p, _i, _sz, _p]
+lib.ozb_scale_residues_cols.argtypes = [_i, _p, _i, _i, _ll, _i, _p, _p, _p, _i, _sz, _p]
+lib.ozb_gemm_i8.argtypes = [_p, _p, _p, _i, _i, _i, _i, _ll, _ll, _ll, _sz, _sz, _sz, _p]
+lib.ozb_gemm_i8_mod.argtypes = [_p, _p, _p, _i, _i, _i, _i, _ll, _ll, _ll, _sz, _sz, _sz, _i, _p]
+lib.ozb_crt_i32.argtypes = [_i, _p, _sz, _i, _i, _ll, _p, _p, _p, _ll, _p]
+lib.ozb_crt_i8.argtypes = [_i, _p, _sz, _i, _i, _ll, _p, _p, _p, _ll, _p]
+lib.ozb_status.argtypes = []
+
+# every symbol include/ozb.h declares; tests check that the library exports each one
+SYMBOLS = [
+    "ozb_version", "ozb_error", "ozb_device", "ozb_dgemm", "ozb_ddgemm", "ozb_tdgemm", "ozb_release", "ozb_bench",
+    "ozb_bits_for", "ozb_modulus", "ozb_plan_create", "ozb_plan_destroy", "ozb_plan_dgemm", "ozb_plan_set_a",
+    "ozb_plan_panel", "ozb_plan_view", "ozb_plan_status", "ozb_plan_phase_ms", "ozb_dgemm_ex",
+    "ozb_scale_residues_rows", "ozb_scale_residues_cols", "ozb_gemm_i8", "ozb_gemm_i8_mod", "ozb_crt_i32", "ozb_crt_i8",
+    "ozb_status",
+]

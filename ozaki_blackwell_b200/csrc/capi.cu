@@ -1,0 +1,386 @@
+// capi.cu -- the C ABI (include/ozb.h) and the plan/driver layer behind it.
+//
+// Mirrors the reference's python/capi.cu (argument checks, error codes, one mutex, one cached plan per precision, host
+// staging, the built-in benchmark) and src/ozaki2.cuh:116-164 (Plan, plan, release, dgemm), over this library's own
+// kernels. There is no CPU path: every entry point that computes needs a compute-capability-10 device and fails with
+// OZB_EARCH otherwise.
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include "../../include/ozb.h"
+#include "oz_common.cuh"
+#include "oz_kernels.h"
+
+#define OZB_API extern "C" __attribute__((visibility("default")))
+#ifndef OZB_VERSION
+#define OZB_VERSION "0.1.0-b200"
+#endif
+
+using namespace ozk;
+
+// ---------------------------------------------------------------------------------------------------------------
+// plan
+// ---------------------------------------------------------------------------------------------------------------
+struct ozb_plan {
+    int M, N, K, nm, bits, maxbits;
+    int Kp, Np;                      // pitch of the residue planes of A and B (bytes); pitch of the product planes (bytes)
+    size_t planeA, planeB, planeC;   // plane pitches in bytes
+    int8_t *Ar, *Br, *Cr;
+    int *sa, *sb, *status;
+    unsigned long long *colmax;
+    cudaStream_t last;
+    bool prof;
+    cudaEvent_t ev[4];
+    float ms[3];
+    bool have_ms;
+};
+
+static int round_up(int x, int to) { return (x + to - 1) / to * to; }
+
+static int bits_for_impl(int nm, int K, int maxbits) {   // src/ozaki2.cuh:101-108, with the abort turned into -1
+    double log2P = 0;
+    for (int l = 0; l < nm; l++) log2P += log2((double)modulus(l));
+    if (K >= 131072) return -1;
+    const int b = (int)floor((log2P - 2 - log2((double)K)) / 2);
+    return b > maxbits ? maxbits : b;
+}
+
+static void plan_free(ozb_plan *p) {
+    if (!p) return;
+    cudaFree(p->Ar); cudaFree(p->Br); cudaFree(p->Cr); cudaFree(p->sa); cudaFree(p->sb); cudaFree(p->status); cudaFree(p->colmax);
+    if (p->prof) for (auto &e : p->ev) cudaEventDestroy(e);
+    delete p;
+}
+
+static int plan_make(int M, int N, int K, int nm, int maxbits, ozb_plan **out) {
+    ozb_plan *p = new ozb_plan();
+    memset(p, 0, sizeof *p);
+    p->M = M; p->N = N; p->K = K; p->nm = nm; p->maxbits = maxbits;
+    p->bits = bits_for_impl(nm, K, maxbits);
+    p->Kp = round_up(K, 128);   // rows start on 128-byte lines; the TMA extent is K itself, so the padding is never read
+    p->Np = round_up(N, 16);
+    p->planeA = (size_t)M * p->Kp; p->planeB = (size_t)N * p->Kp; p->planeC = (size_t)M * p->Np;
+    cudaError_t e = cudaMalloc(&p->Ar, nm * p->planeA);
+    if (!e) e = cudaMalloc(&p->Br, nm * p->planeB);
+    if (!e) e = cudaMalloc(&p->Cr, nm * p->planeC);
+    if (!e) e = cudaMalloc(&p->sa, (size_t)M * 4);
+    if (!e) e = cudaMalloc(&p->sb, (size_t)N * 4);
+    if (!e) e = cudaMalloc(&p->colmax, (size_t)N * 8);
+    if (!e) e = cudaMalloc(&p->status, 4);
+    if (!e) e = cudaMemset(p->status, 0, 4);
+    p->prof = getenv("OZ_PROF") != nullptr;
+    if (!e && p->prof) for (auto &ev : p->ev) if (!e) e = cudaEventCreate(&ev);
+    if (e) { cudaGetLastError(); p->prof = false; plan_free(p); return (int)e; }
+    *out = p;
+    return 0;
+}
+
+static int plan_set_a(ozb_plan *p, const double *A, long long lda, cudaStream_t st) {
+    p->last = st;
+    return (int)scale_residues_rows(p->nm, A, p->M, p->K, lda, p->bits, p->sa, p->Ar, p->Kp, p->planeA, st);
+}
+// columns [j0, j0 + n) of B and C; B and C point at column j0
+static int plan_panel(ozb_plan *p, const double *B, long long ldb, double *C, long long ldc, int j0, int n, cudaStream_t st,
+                      bool timed) {
+    p->last = st;
+    int8_t *Br = p->Br + (size_t)j0 * p->Kp, *Cr = p->Cr + j0;
+    cudaError_t e = scale_residues_cols(p->nm, B, p->K, n, ldb, p->bits, p->colmax + j0, p->sb + j0, Br, p->Kp, p->planeB, st);
+    if (e) return (int)e;
+    if (timed) cudaEventRecord(p->ev[1], st);
+    // the epilogue writes whole 16-byte pieces: the panel's pitch view must allow n rounded up to 16 inside Np
+    e = gemm_i8_planes(p->Ar, Br, Cr, p->M, n, p->K, p->nm, p->Kp, p->Kp, p->Np, p->planeA, p->planeB, p->planeC, 1, 0,
+                       p->status, 0, st);
+    if (e) return (int)e;
+    if (timed) cudaEventRecord(p->ev[2], st);
+    e = crt_from_i8(p->nm, Cr, p->planeC, p->M, n, p->Np, p->sa, p->sb + j0, C, ldc, st);
+    return (int)e;
+}
+static int plan_dgemm(ozb_plan *p, const double *A, long long lda, const double *B, long long ldb, double *C, long long ldc,
+                      cudaStream_t st) {
+    p->have_ms = false;
+    if (p->prof) cudaEventRecord(p->ev[0], st);
+    if (int e = plan_set_a(p, A, lda, st)) return e;
+    if (int e = plan_panel(p, B, ldb, C, ldc, 0, p->N, st, p->prof)) return e;
+    if (p->prof) {   // src/ozaki2.cuh:147-152: one line per product on stderr
+        cudaEventRecord(p->ev[3], st);
+        cudaEventSynchronize(p->ev[3]);
+        for (int i = 0; i < 3; i++) cudaEventElapsedTime(&p->ms[i], p->ev[i], p->ev[i + 1]);
+        p->have_ms = true;
+        fprintf(stderr, "oz%d %dx%dx%d: scale+residues %.3f  INT8 GEMMs %.3f (%.0f TOPS)  CRT %.3f ms\n", p->nm, p->M, p->N, p->K,
+                p->ms[0], p->ms[1], 2.0 * p->nm * p->M * (double)p->N * p->K / (p->ms[1] * 1e9), p->ms[2]);
+    }
+    return 0;
+}
+static int plan_status(ozb_plan *p) {
+    int h = 0;
+    cudaError_t e = cudaStreamSynchronize(p->last);
+    if (!e) e = cudaMemcpy(&h, p->status, 4, cudaMemcpyDeviceToHost);
+    if (e) return (int)e;
+    if (h) { cudaMemset(p->status, 0, 4); return OZB_ETIMEOUT; }
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// the reference's ABI
+// ---------------------------------------------------------------------------------------------------------------
+namespace {
+std::mutex mu;
+struct Cache { ozb_plan *p = nullptr; };
+Cache cache[3];   // 0 FP64, 1 double-double, 2 triple-double (python/capi.cu:21)
+int *stage_status[64] = {};   // one status word per device for the stage calls
+
+int check_args(int M, int N, int K) {   // python/capi.cu:23-29
+    if (M <= 0 || N <= 0 || K <= 0) return OZB_EARG;
+    if (K >= 131072) return OZB_EK;
+    int dev, major;
+    if (cudaGetDevice(&dev) || cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev)) return (int)cudaGetLastError();
+    return major != 10 ? OZB_EARCH : 0;   // tcgen05 / tensor memory: this binary holds sm_100a code only
+}
+int plan_for(int which, int M, int N, int K, int nm, int maxbits, ozb_plan **out) {   // python/capi.cu:30-35
+    Cache &c = cache[which];
+    if (c.p && (c.p->M != M || c.p->N != N || c.p->K != K || c.p->nm != nm || c.p->maxbits != maxbits)) { plan_free(c.p); c.p = nullptr; }
+    if (!c.p) if (int e = plan_make(M, N, K, nm, maxbits, &c.p)) { c.p = nullptr; return e; }
+    *out = c.p;
+    return 0;
+}
+int finish() { const int e = (int)cudaDeviceSynchronize(); return e ? e : (int)cudaGetLastError(); }   // python/capi.cu:49
+int *status_word() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) || dev < 0 || dev >= 64) return nullptr;
+    if (!stage_status[dev]) {
+        if (cudaMalloc(&stage_status[dev], 4) || cudaMemset(stage_status[dev], 0, 4)) { cudaGetLastError(); stage_status[dev] = nullptr; }
+    }
+    return stage_status[dev];
+}
+}  // namespace
+
+OZB_API const char *ozb_version(void) { return OZB_VERSION; }
+
+OZB_API const char *ozb_error(int e) {
+    switch (e) {
+    case 0: return "ok";
+    case OZB_EARG: return "M, N and K must be positive";
+    case OZB_EK: return "K must be below 131072 (the int32 accumulators of the INT8 GEMMs)";
+    case OZB_EARCH: return "this build runs on compute capability 10.x GPUs (B200, sm_100a: tcgen05 tensor cores) only";
+    case OZB_ETIMEOUT: return "a bounded wait inside the INT8 GEMM kernel expired; the result is not valid";
+    case OZB_ENOTBUILT: return "this entry point is exported for ABI compatibility but not built in this library";
+    case OZB_ESIZE: return "a size exceeds the fixed limit of this entry point";
+    default: return cudaGetErrorString((cudaError_t)e);
+    }
+}
+
+OZB_API int ozb_device(char *name, int len, int *sm, int *l2_kib, int *sms) {
+    int dev; cudaDeviceProp p;
+    if (int e = cudaGetDevice(&dev)) return e;
+    if (int e = cudaGetDeviceProperties(&p, dev)) return e;
+    if (name && len > 0) { strncpy(name, p.name, len - 1); name[len - 1] = 0; }
+    if (sm) *sm = 10 * p.major + p.minor;
+    if (l2_kib) *l2_kib = p.l2CacheSize >> 10;
+    if (sms) *sms = p.multiProcessorCount;
+    return 0;
+}
+
+OZB_API int ozb_dgemm(int M, int N, int K, const double *A, const double *B, double *C, int moduli, int on_host) {
+    if (int e = check_args(M, N, K)) return e;
+    if (moduli < 8 || moduli > 16) return OZB_EARG;
+    std::lock_guard<std::mutex> g(mu);
+    ozb_plan *p;
+    if (int e = plan_for(0, M, N, K, moduli, 62, &p)) return e;
+    if (!on_host) {
+        if (int e = plan_dgemm(p, A, K, B, N, C, N, 0)) return e;
+        if (int e = finish()) return e;
+        return plan_status(p);
+    }
+    // host operands: stage through device buffers (python/capi.cu:37-48,82-88)
+    double *dA = nullptr, *dB = nullptr, *dC = nullptr;
+    const size_t la = (size_t)M * K * 8, lb = (size_t)K * N * 8, lc = (size_t)M * N * 8;
+    int e = (int)cudaMalloc(&dA, la);
+    if (!e) e = (int)cudaMalloc(&dB, lb);
+    if (!e) e = (int)cudaMalloc(&dC, lc);
+    if (!e) e = (int)cudaMemcpy(dA, A, la, cudaMemcpyHostToDevice);
+    if (!e) e = (int)cudaMemcpy(dB, B, lb, cudaMemcpyHostToDevice);
+    if (!e) e = plan_dgemm(p, dA, K, dB, N, dC, N, 0);
+    if (!e) e = finish();
+    if (!e) e = plan_status(p);
+    if (!e) e = (int)cudaMemcpy(C, dC, lc, cudaMemcpyDeviceToHost);
+    cudaFree(dA); cudaFree(dB); cudaFree(dC);
+    return e;
+}
+
+OZB_API int ozb_ddgemm(int M, int N, int K, const double *, const double *, const double *, const double *, double *, double *, int) {
+    if (int e = check_args(M, N, K)) return e;
+    return OZB_ENOTBUILT;
+}
+
+OZB_API int ozb_tdgemm(int M, int N, int K, const double *, const double *, const double *, const double *, const double *,
+                       const double *, double *, double *, double *, int) {
+    if (int e = check_args(M, N, K)) return e;
+    return OZB_ENOTBUILT;
+}
+
+OZB_API void ozb_release(void) {
+    std::lock_guard<std::mutex> g(mu);
+    for (Cache &c : cache) if (c.p) { plan_free(c.p); c.p = nullptr; }
+}
+
+OZB_API int ozb_bench(int n, int kind, int reps, double *median_ms) {   // python/capi.cu:130-164
+    if (int e = check_args(n, n, n)) return e;
+    if (kind < 0 || kind > 2 || reps < 1 || reps > 101 || !median_ms) return OZB_EARG;
+    if (kind != 0) return OZB_ENOTBUILT;
+    const size_t len = (size_t)n * n;
+    double *d[3] = {};
+    int err = 0;
+    for (int i = 0; i < 3 && !err; i++) err = (int)cudaMalloc(&d[i], len * sizeof(double));
+    if (!err) {   // values in [-1, 1) from the fixed xorshift hash of the reference (python/capi.cu:140-145)
+        double *h = (double *)malloc(len * sizeof(double));
+        if (!h) err = (int)cudaErrorMemoryAllocation;
+        for (int i = 0; i < 2 && !err; i++) {
+            uint64_t x = 0x9E3779B97F4A7C15ull * (i + 1);
+            for (size_t j = 0; j < len; j++) { x ^= x << 13; x ^= x >> 7; x ^= x << 17; h[j] = (double)(x >> 11) * 0x1p-52 - 1.0; }
+            err = (int)cudaMemcpy(d[i == 0 ? 0 : 2], h, len * sizeof(double), cudaMemcpyHostToDevice);
+        }
+        free(h);
+    }
+    float t[101]; int nt = 0;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    if (!err) { cudaEventCreate(&e0); cudaEventCreate(&e1); }
+    for (int r = -1; r < reps && !err; r++) {   // r = -1: warm-up (plan, first launches)
+        cudaEventRecord(e0);
+        err = ozb_dgemm(n, n, n, d[0], d[2], d[1], 16, 0);
+        cudaEventRecord(e1); cudaEventSynchronize(e1);
+        float ms; cudaEventElapsedTime(&ms, e0, e1);
+        if (r >= 0) t[nt++] = ms;
+    }
+    if (nt) {
+        for (int i = 1; i < nt; i++) for (int j = i; j > 0 && t[j - 1] > t[j]; j--) { const float x = t[j]; t[j] = t[j - 1]; t[j - 1] = x; }
+        *median_ms = t[nt / 2];
+    }
+    if (e0) { cudaEventDestroy(e0); cudaEventDestroy(e1); }
+    for (double *p : d) if (p) cudaFree(p);
+    return err;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// additions
+// ---------------------------------------------------------------------------------------------------------------
+OZB_API int ozb_bits_for(int nm, int K, int maxbits) { return (nm < 1 || nm > MAXM || K <= 0) ? -1 : bits_for_impl(nm, K, maxbits); }
+OZB_API int ozb_modulus(int l) { return (l >= 0 && l < MAXM) ? modulus(l) : 0; }
+
+OZB_API int ozb_plan_create(int M, int N, int K, int moduli, int maxbits, ozb_plan **out) {
+    if (!out) return OZB_EARG;
+    if (int e = check_args(M, N, K)) return e;
+    if (moduli < 8 || moduli > 16) return OZB_EARG;
+    std::lock_guard<std::mutex> g(mu);
+    return plan_make(M, N, K, moduli, maxbits, out);
+}
+OZB_API void ozb_plan_destroy(ozb_plan *p) {
+    std::lock_guard<std::mutex> g(mu);
+    plan_free(p);
+}
+OZB_API int ozb_plan_dgemm(ozb_plan *p, const double *A, long long lda, const double *B, long long ldb, double *C, long long ldc,
+                           void *stream) {
+    if (!p || !A || !B || !C || lda < p->K || ldb < p->N || ldc < p->N) return OZB_EARG;
+    std::lock_guard<std::mutex> g(mu);
+    return plan_dgemm(p, A, lda, B, ldb, C, ldc, (cudaStream_t)stream);
+}
+OZB_API int ozb_plan_set_a(ozb_plan *p, const double *A, long long lda, void *stream) {
+    if (!p || !A || lda < p->K) return OZB_EARG;
+    std::lock_guard<std::mutex> g(mu);
+    return plan_set_a(p, A, lda, (cudaStream_t)stream);
+}
+OZB_API int ozb_plan_panel(ozb_plan *p, const double *B, long long ldb, double *C, long long ldc, int j0, int ncols, void *stream) {
+    if (!p || !B || !C || j0 < 0 || (j0 & 255) || ncols <= 0 || j0 + ncols > p->N || ldb < ncols || ldc < ncols) return OZB_EARG;
+    std::lock_guard<std::mutex> g(mu);
+    return plan_panel(p, B, ldb, C, ldc, j0, ncols, (cudaStream_t)stream, false);
+}
+OZB_API int ozb_plan_view(ozb_plan *p, int *bits, int *Kp, int *Np, int8_t **Ar, int8_t **Br, int8_t **Cr, int **sa, int **sb) {
+    if (!p) return OZB_EARG;
+    if (bits) *bits = p->bits;
+    if (Kp) *Kp = p->Kp;
+    if (Np) *Np = p->Np;
+    if (Ar) *Ar = p->Ar;
+    if (Br) *Br = p->Br;
+    if (Cr) *Cr = p->Cr;
+    if (sa) *sa = p->sa;
+    if (sb) *sb = p->sb;
+    return 0;
+}
+OZB_API int ozb_plan_status(ozb_plan *p) {
+    if (!p) return OZB_EARG;
+    std::lock_guard<std::mutex> g(mu);
+    return plan_status(p);
+}
+OZB_API int ozb_plan_phase_ms(ozb_plan *p, float ms[3]) {
+    if (!p || !ms || !p->have_ms) return OZB_EARG;
+    for (int i = 0; i < 3; i++) ms[i] = p->ms[i];
+    return 0;
+}
+
+OZB_API int ozb_dgemm_ex(int M, int N, int K, const double *A, long long lda, const double *B, long long ldb, double *C,
+                         long long ldc, int moduli, void *stream) {
+    if (int e = check_args(M, N, K)) return e;
+    if (moduli < 8 || moduli > 16 || !A || !B || !C || lda < K || ldb < N || ldc < N) return OZB_EARG;
+    std::lock_guard<std::mutex> g(mu);
+    ozb_plan *p;
+    if (int e = plan_for(0, M, N, K, moduli, 62, &p)) return e;
+    return plan_dgemm(p, A, lda, B, ldb, C, ldc, (cudaStream_t)stream);
+}
+
+OZB_API int ozb_scale_residues_rows(int moduli, const double *X, int rows, int len, long long ldx, int bits, int *s, int8_t *R,
+                                    int ld, size_t plane, void *stream) {
+    if (int e = check_args(rows, 1, len)) return e;
+    if (moduli < 8 || moduli > 16 || !X || !s || !R || ldx < len || ld < round_up(len, 4) || (ld & 3) || (plane & 3)) return OZB_EARG;
+    return (int)scale_residues_rows(moduli, X, rows, len, ldx, bits, s, R, ld, plane, (cudaStream_t)stream);
+}
+OZB_API int ozb_scale_residues_cols(int moduli, const double *X, int rows, int cols, long long ldx, int bits, void *colmax, int *s,
+                                    int8_t *R, int ld, size_t plane, void *stream) {
+    if (int e = check_args(1, cols, rows)) return e;
+    if (moduli < 8 || moduli > 16 || !X || !s || !R || !colmax || ldx < cols || ld < round_up(rows, 16) || (ld & 15) || (plane & 15) ||
+        (reinterpret_cast<uintptr_t>(R) & 15))
+        return OZB_EARG;
+    return (int)scale_residues_cols(moduli, X, rows, cols, ldx, bits, (unsigned long long *)colmax, s, R, ld, plane, (cudaStream_t)stream);
+}
+OZB_API int ozb_gemm_i8(const int8_t *A, const int8_t *Bt, int32_t *C, int M, int N, int K, int Z, long long lda, long long ldb,
+                        long long ldc, size_t plane_a, size_t plane_b, size_t plane_c, void *stream) {
+    if (int e = check_args(M, N, K)) return e;
+    if (!A || !Bt || !C || Z <= 0 || lda < K || ldb < K || ldc < N) return OZB_EARG;
+    int *st = status_word();
+    if (!st) return (int)cudaErrorMemoryAllocation;
+    return (int)gemm_i8_planes(A, Bt, C, M, N, K, Z, lda, ldb, ldc, plane_a, plane_b, plane_c, 0, 0, st, 0, (cudaStream_t)stream);
+}
+OZB_API int ozb_gemm_i8_mod(const int8_t *A, const int8_t *Bt, int8_t *C, int M, int N, int K, int Z, long long lda, long long ldb,
+                            long long ldc, size_t plane_a, size_t plane_b, size_t plane_c, int first_modulus, void *stream) {
+    if (int e = check_args(M, N, K)) return e;
+    if (!A || !Bt || !C || Z <= 0 || lda < K || ldb < K || ldc < round_up(N, 16) || (plane_c & 15) ||
+        (reinterpret_cast<uintptr_t>(C) & 15))
+        return OZB_EARG;
+    int *st = status_word();
+    if (!st) return (int)cudaErrorMemoryAllocation;
+    return (int)gemm_i8_planes(A, Bt, C, M, N, K, Z, lda, ldb, ldc, plane_a, plane_b, plane_c, 1, first_modulus, st, 0,
+                               (cudaStream_t)stream);
+}
+OZB_API int ozb_crt_i32(int moduli, const int32_t *Cl, size_t plane, int M, int N, long long ldr, const int *sa, const int *sb,
+                        double *C, long long ldc, void *stream) {
+    if (int e = check_args(M, N, 1)) return e;
+    if (moduli < 8 || moduli > 16 || !Cl || !sa || !sb || !C || ldr < N || ldc < N) return OZB_EARG;
+    return (int)crt_from_i32(moduli, Cl, plane, M, N, ldr, sa, sb, C, ldc, (cudaStream_t)stream);
+}
+OZB_API int ozb_crt_i8(int moduli, const int8_t *Cr, size_t plane, int M, int N, long long ldr, const int *sa, const int *sb,
+                       double *C, long long ldc, void *stream) {
+    if (int e = check_args(M, N, 1)) return e;
+    if (moduli < 8 || moduli > 16 || !Cr || !sa || !sb || !C || ldr < round_up(N, 4) || (ldr & 3) || (plane & 3) ||
+        (reinterpret_cast<uintptr_t>(Cr) & 3) || ldc < N)
+        return OZB_EARG;
+    return (int)crt_from_i8(moduli, Cr, plane, M, N, ldr, sa, sb, C, ldc, (cudaStream_t)stream);
+}
+OZB_API int ozb_status(void) {
+    if (int e = (int)cudaDeviceSynchronize()) return e;
+    int *st = status_word();
+    if (!st) return (int)cudaErrorMemoryAllocation;
+    int h = 0;
+    if (int e = (int)cudaMemcpy(&h, st, 4, cudaMemcpyDeviceToHost)) return e;
+    if (h) { cudaMemset(st, 0, 4); return OZB_ETIMEOUT; }
+    return 0;
+}

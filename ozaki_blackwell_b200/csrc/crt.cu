@@ -1,0 +1,153 @@
+// crt.cu -- kernel 4 of the FP64 product: Chinese-remainder reconstruction back to FP64.
+//
+// What it computes is the reference's `crt<NM>` (src/ozaki2.cuh:82-97): per output element the balanced residues of the
+// nm exact products, Garner's balanced mixed-radix digits x_0..x_{nm-1}, then
+//     y = x_{nm-1};  y = fma(y, m_l, x_l) for l = nm-2 .. 0   (IEEE double: the sequence of roundings is part of the result)
+//     C[i][j] = ldexp(y, -(sa[i] + sb[j])).
+//
+// How: the reference spends l modular reductions on digit l (120 at 16 moduli). Here the recurrence is unrolled into one
+// signed dot product per digit (see garner_p / garner_q in oz_tables.cuh), evaluated with dp4a on digits packed four to
+// a register, and reduced once: 39 dp4a and 15 multiply-high reductions per element. The digits are the same integers
+// (a balanced digit is unique in its residue class), so the FP64 Horner loop sees the same operands in the same order.
+// Input is either the GEMM epilogue's int8 planes of already balanced residues (16 bytes per element at 16 moduli
+// instead of 64) or, for the reference's layout, int32 planes of raw products.
+#include "oz_common.cuh"
+
+namespace ozk {
+
+// 4 x 4 byte transpose: in[p] holds plane p of elements 0..3; out[e] holds planes 0..3 of element e
+__device__ __forceinline__ void transpose4x4(const uint32_t (&in)[4], uint32_t (&out)[4]) {
+    const uint32_t a = __byte_perm(in[0], in[1], 0x5140), b = __byte_perm(in[0], in[1], 0x7362);   // (p0e0 p1e0 p0e1 p1e1), (.. e2 e3)
+    const uint32_t c = __byte_perm(in[2], in[3], 0x5140), d = __byte_perm(in[2], in[3], 0x7362);
+    out[0] = __byte_perm(a, c, 0x5410);
+    out[1] = __byte_perm(a, c, 0x7632);
+    out[2] = __byte_perm(b, d, 0x5410);
+    out[3] = __byte_perm(b, d, 0x7632);
+}
+
+// One element: X[g] holds the balanced residues r_{4g}..r_{4g+3} as int8 (unused bytes zero). Returns y of the Horner loop.
+template <int NM>
+__device__ __forceinline__ double garner_horner(uint32_t (&X)[(NM + 3) / 4]) {
+    double d[NM];
+    d[0] = (double)(int)(int8_t)(X[0] & 255);   // modulus 256: the residue is the digit
+    static_for<1, NM>([&](auto L) {
+        constexpr int l = decltype(L)::value, m = modulus(l);
+        constexpr int lift = lift_of(l, GARNER_BOUND);
+        static_assert(magic_ok(l, (uint64_t)lift + GARNER_BOUND), "multiply-high reduction out of range");
+        int acc = lift;
+        // digits x_0..x_{l-1} have already replaced the residues in the low bytes; byte l still holds r_l
+        static_for<0, l / 4 + 1>([&](auto G) {
+            constexpr int g = decltype(G)::value;
+            constexpr auto coef = [](int idx) constexpr { return idx < l ? garner_q(idx, l) : (idx == l ? garner_p(l) : 0); };
+            constexpr uint32_t cw = pack4(coef(4 * g), coef(4 * g + 1), coef(4 * g + 2), coef(4 * g + 3));
+            acc = dp4a_ss(X[g], cw, acc);
+        });
+        const uint32_t r = mod_magic<l>((uint32_t)acc);            // (x_l + floor(m/2)) in [0, m)
+        const uint32_t xl = r - (uint32_t)half_of(l);
+        constexpr uint32_t sel = l % 4 == 0 ? 0x3214u : l % 4 == 1 ? 0x3240u : l % 4 == 2 ? 0x3410u : 0x4210u;
+        X[l / 4] = __byte_perm(X[l / 4], xl, sel);                  // byte l%4 <- low byte of xl
+        // 2^52 + r is exact in the low word of a double with exponent 2^52; subtracting 2^52 + floor(m/2) leaves x_l
+        d[l] = __hiloint2double(0x43300000, (int)r) - (4503599627370496.0 + (double)half_of(l));
+        (void)m;
+    });
+    double y = d[NM - 1];
+#pragma unroll
+    for (int l = NM - 2; l >= 0; l--) y = fma(y, (double)modulus(l), d[l]);
+    return y;
+}
+
+// balanced residue of a raw int32 product (reference layout of the planes)
+template <int L>
+__device__ __forceinline__ int balanced_of_i32(int32_t x) {
+    constexpr int m = modulus(L);
+    int r = x % m;
+    if (r < 0) r += m;
+    return r >= (m + 1) / 2 ? r - m : r;
+}
+
+// Each thread reconstructs four consecutive columns of one row.
+// In = int8_t: planes of balanced residues, row pitch ldr bytes (multiple of 4), plane pitch `plane` bytes.
+// In = int32_t: planes of raw products, row pitch ldr elements, plane pitch `plane` elements.
+template <int NM, class In>
+__global__ void __launch_bounds__(256) crt_kernel(const In *__restrict__ Cp, size_t plane, int M, int N, long long ldr,
+                                                  const int *__restrict__ sa, const int *__restrict__ sb,
+                                                  double *__restrict__ C, long long ldc) {
+    constexpr int G = (NM + 3) / 4;
+    const int i = blockIdx.x;
+    const int j0 = (blockIdx.y * 256 + threadIdx.x) * 4;
+    if (j0 >= N) return;
+    uint32_t E[4][G];   // E[e][g]: residues 4g..4g+3 of element j0 + e
+    if constexpr (sizeof(In) == 1) {
+        const int8_t *base = reinterpret_cast<const int8_t *>(Cp) + (size_t)i * ldr + j0;
+#pragma unroll
+        for (int g = 0; g < G; g++) {
+            uint32_t w[4], t[4];
+#pragma unroll
+            for (int p = 0; p < 4; p++)
+                w[p] = 4 * g + p < NM ? __ldg(reinterpret_cast<const uint32_t *>(base + (size_t)(4 * g + p) * plane)) : 0u;
+            transpose4x4(w, t);
+#pragma unroll
+            for (int e = 0; e < 4; e++) E[e][g] = t[e];
+        }
+    } else {
+        const int32_t *base = reinterpret_cast<const int32_t *>(Cp) + (size_t)i * ldr + j0;
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+#pragma unroll
+            for (int g = 0; g < G; g++) E[e][g] = 0;
+            if (j0 + e < N) {
+                static_for<0, NM>([&](auto L) {
+                    constexpr int l = decltype(L)::value;
+                    const int r = balanced_of_i32<l>(base[(size_t)l * plane + e]);
+                    E[e][l / 4] |= (uint32_t)(r & 255) << (8 * (l % 4));
+                });
+            }
+        }
+    }
+    const int si = sa[i];
+    double out[4];
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+        const double y = garner_horner<NM>(E[e]);
+        out[e] = j0 + e < N ? ldexp(y, -(si + sb[j0 + e])) : 0.0;
+    }
+    double *dst = C + (size_t)i * ldc + j0;
+    if (j0 + 3 < N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+        reinterpret_cast<double2 *>(dst)[0] = make_double2(out[0], out[1]);
+        reinterpret_cast<double2 *>(dst)[1] = make_double2(out[2], out[3]);
+    } else {
+#pragma unroll
+        for (int e = 0; e < 4; e++)
+            if (j0 + e < N) dst[e] = out[e];
+    }
+}
+
+template <int NM, class In>
+static cudaError_t launch_crt_t(const In *Cp, size_t plane, int M, int N, long long ldr, const int *sa, const int *sb, double *C,
+                                long long ldc, cudaStream_t st) {
+    crt_kernel<NM, In><<<dim3(M, (N + 1023) / 1024), 256, 0, st>>>(Cp, plane, M, N, ldr, sa, sb, C, ldc);
+    return cudaGetLastError();
+}
+
+#define OZ_DISPATCH_NM(nm, CALL)                                                                                  \
+    switch (nm) {                                                                                                 \
+    case 8: { constexpr int NM = 8; return CALL; }    case 9: { constexpr int NM = 9; return CALL; }              \
+    case 10: { constexpr int NM = 10; return CALL; }  case 11: { constexpr int NM = 11; return CALL; }            \
+    case 12: { constexpr int NM = 12; return CALL; }  case 13: { constexpr int NM = 13; return CALL; }            \
+    case 14: { constexpr int NM = 14; return CALL; }  case 15: { constexpr int NM = 15; return CALL; }            \
+    case 16: { constexpr int NM = 16; return CALL; }                                                              \
+    default: return cudaErrorInvalidValue;                                                                        \
+    }
+
+// planes of balanced int8 residues [nm][M][ldr] (ldr a multiple of 4, rows readable up to the next multiple of 4 columns)
+cudaError_t crt_from_i8(int nm, const int8_t *Cr, size_t plane, int M, int N, long long ldr, const int *sa, const int *sb,
+                        double *C, long long ldc, cudaStream_t st) {
+    OZ_DISPATCH_NM(nm, (launch_crt_t<NM, int8_t>(Cr, plane, M, N, ldr, sa, sb, C, ldc, st)));
+}
+// planes of raw int32 products [nm][M][ldr], the reference's layout (src/ozaki2.cuh:146)
+cudaError_t crt_from_i32(int nm, const int32_t *Cl, size_t plane, int M, int N, long long ldr, const int *sa, const int *sb,
+                         double *C, long long ldc, cudaStream_t st) {
+    OZ_DISPATCH_NM(nm, (launch_crt_t<NM, int32_t>(Cl, plane, M, N, ldr, sa, sb, C, ldc, st)));
+}
+
+}  // namespace ozk

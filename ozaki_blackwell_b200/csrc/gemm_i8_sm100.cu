@@ -1,0 +1,361 @@
+// gemm_i8_sm100.cu -- kernel 3 of the FP64 product: the exact INT8 GEMMs, one per modulus, on 5th-generation tensor cores.
+//
+// What it computes is the reference's gemm_i8_run (src/gemm_i8.cuh:148-160): for every plane z < Z
+//     C[z][i][j] = sum_k A[z][i][k] * Bt[z][j][k]       int8 x int8 -> exact int32, both operands K-contiguous
+// and, in the fused mode, what the first line of the reference's crt kernel does to it (src/ozaki2.cuh:88): the balanced
+// residue mod m_z, stored as int8 (one byte per product instead of four).
+//
+// How (sm_100a only): a persistent, warp-specialised kernel, one CTA per SM.
+//   warp 0   producer: TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast) fills a ring of shared-memory stages,
+//            each one 128-byte K-slab of a 128-row A tile and a 256-row B tile, straight from the K-major residue planes
+//            (a 3-D tensor map {k, row, plane}; rows and k beyond the matrix are zero-filled by the hardware).
+//   warp 1   issuer: one thread issues tcgen05.mma kind::i8 (M 128, N 256, K 32 per instruction) from shared-memory
+//            descriptors into one of two 128 x 256 int32 accumulators in tensor memory, and commits each stage back to
+//            the producer and each finished tile to the epilogue through mbarriers.
+//   warps 2-5 epilogue: tcgen05.ld the finished accumulator (one row per thread), reduce mod m_z (or keep int32) and
+//            store, while the issuer is already accumulating the next tile into the other buffer.
+// Work items are (plane, tile) pairs walked plane by plane and, inside a plane, in bands of tile rows so that the A
+// band and the B panels in flight stay in L2. Every mbarrier wait is bounded: on expiry the CTA raises a status word,
+// stops issuing, releases its tensor memory and returns.
+#include <cuda.h>
+#include "oz_common.cuh"
+
+namespace ozk {
+
+namespace g8 {
+constexpr int BM = 128, BN = 256, BKB = 128;       // tile: rows of A, rows of Bt, bytes (= int8 elements) of K per stage
+constexpr int UK = 32;                             // K of one tcgen05.mma kind::i8
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BKB, B_BYTES = BN * BKB, STAGE_BYTES = A_BYTES + B_BYTES;   // 16 KB + 32 KB
+constexpr int ACC_COLS = BN, TMEM_COLS = 512;      // two accumulators of 256 columns
+constexpr int THREADS = 192;                       // producer warp, issuer warp, four epilogue warps
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr unsigned long long WAIT_NS = 4000000000ull;   // give up on a barrier after 4 s
+
+// instruction descriptor of tcgen05.mma kind::i8: D = S32, A = B = signed 8-bit, both K-major, N = 256, M = 128
+constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long now_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait: each wait has its own budget, started the first time the spin loop looks at the clock. Returns false
+// when the budget ran out or another role of this CTA already gave up (*abort_flag != 0).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    unsigned long long deadline = 0;
+    for (uint32_t spin = 0;; spin++) {
+        if (mbar_try(bar, parity)) return true;
+        if ((spin & 1023u) == 1023u) {
+            if (*abort_flag) return false;
+            const unsigned long long t = now_ns();
+            if (!deadline) deadline = t + WAIT_NS;
+            else if (t > deadline) { *abort_flag = 1; return false; }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, int c0, int c1, int c2, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+
+// shared-memory matrix descriptor: K-major, 128-byte swizzle; rows are 128 bytes, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(IDESC), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr) : "memory");
+}
+
+struct Params {
+    int M, N, K, Z;               // rows of A, rows of Bt, inner length, planes
+    int tiles_m, tiles_n, band;   // tile grid of one plane and the band height (tile rows)
+    int first_modulus;            // plane z reduces mod modulus(first_modulus + z) in the fused mode
+    void *C;                      // int32 [Z][M][ldc] or int8 [Z][M][ldc]
+    long long ldc;                // row pitch of C in elements
+    size_t plane_c;               // plane pitch of C in elements
+    int *status;                  // device word: set to 1 when a wait timed out
+};
+
+__constant__ ModConsts c_modc[MAXM];
+constexpr bool epilogue_reduction_exact() {
+    for (int l = 0; l < MAXM; l++)
+        if (!magic_ok(l, epi_umax(l))) return false;
+    return true;
+}
+static_assert(epilogue_reduction_exact(), "multiply-high reduction out of range for some modulus");
+
+// work item w -> (plane, tile row, tile column): planes outermost, then bands of `band` tile rows walked column by column
+__device__ __forceinline__ void decode_work(const Params &p, int w, int &z, int &tm, int &tn) {
+    const int per_plane = p.tiles_m * p.tiles_n;
+    z = w / per_plane;
+    const int idx = w - z * per_plane, span = p.band * p.tiles_n, first = idx / span * p.band;
+    const int rows = min(p.band, p.tiles_m - first), within = idx - (idx / span) * span;
+    tm = first + within % rows;
+    tn = within / rows;
+}
+
+template <bool FUSED_MOD>
+__global__ void __launch_bounds__(THREADS, 1) gemm_i8_tc(const __grid_constant__ CUtensorMap mapA,
+                                                         const __grid_constant__ CUtensorMap mapB, const Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;          // swizzled tiles need 1024-byte alignment
+    const uint32_t bars = base + STAGES * STAGE_BYTES;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+    auto accfull_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
+    auto accempty_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
+    const uint32_t tmem_slot = bars + 8u * (2 * STAGES + 4);
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < STAGES; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int a = 0; a < 2; a++) { mbar_init(accfull_bar(a), 1); mbar_init(accempty_bar(a), 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {   // the issuer warp owns the tensor memory
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"((uint32_t)TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    uint32_t tmem_base;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
+
+    const int total = p.tiles_m * p.tiles_n * p.Z;
+    const int kblocks = (p.K + BKB - 1) / BKB;
+    volatile int *abortp = &abort_flag;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t it = 0;   // running stage counter
+            for (int w = blockIdx.x; w < total && !*abortp; w += gridDim.x) {
+                int z, tm, tn;
+                decode_work(p, w, z, tm, tn);
+                for (int kb = 0; kb < kblocks; kb++, it++) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(empty_bar(s), ((it / STAGES) & 1u) ^ 1u, abortp)) break;
+                    mbar_expect_tx(full_bar(s), STAGE_BYTES);
+                    const uint32_t sa = base + s * STAGE_BYTES;
+                    tma_load_3d(sa, &mapA, kb * BKB, tm * BM, z, full_bar(s));
+                    tma_load_3d(sa + A_BYTES, &mapB, kb * BKB, tn * BN, z, full_bar(s));
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            uint32_t it = 0, n = 0;   // stage counter, tile counter of this CTA
+            for (int w = blockIdx.x; w < total && !*abortp; w += gridDim.x, n++) {
+                const uint32_t acc = n & 1u;
+                if (!mbar_wait(accempty_bar(acc), ((n >> 1) & 1u) ^ 1u, abortp)) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
+                bool ok = true;
+                for (int kb = 0; kb < kblocks; kb++, it++) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(full_bar(s), (it / STAGES) & 1u, abortp)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t sa = base + s * STAGE_BYTES;
+                    const uint64_t da = smem_desc(sa), db = smem_desc(sa + A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BKB / UK; k++)   // +32 bytes of K inside the swizzled row = +2 in the address field
+                        mma_i8(d_tmem, da + 2u * k, db + 2u * k, (kb | k) != 0);
+                    mma_commit(empty_bar(s));            // the stage is free once these MMAs have read it
+                }
+                if (!ok) break;
+                mma_commit(accfull_bar(acc));            // the accumulator is complete once all MMAs above retire
+            }
+        }
+    } else {
+        const int q = warp & 3;                          // a warp may only touch TMEM lanes 32 (warp % 4) .. +31
+        ModConsts mc{};
+        uint32_t n = 0;
+        for (int w = blockIdx.x; w < total && !*abortp; w += gridDim.x, n++) {
+            int z, tm, tn;
+            decode_work(p, w, z, tm, tn);
+            const uint32_t acc = n & 1u;
+            if constexpr (FUSED_MOD) mc = c_modc[p.first_modulus + z];
+            // every lane waits (each needs the barrier's acquire); the vote keeps the warp together if one gave up
+            if (!__all_sync(~0u, mbar_wait(accfull_bar(acc), (n >> 1) & 1u, abortp))) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int row = tm * BM + q * 32 + lane;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * ACC_COLS;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; c++) {
+                uint32_t v[32];
+                tmem_ld32(taddr + c * 32, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                const int col = tn * BN + c * 32;
+                if (row < p.M && col < p.N) {
+                    if constexpr (FUSED_MOD) {
+                        uint32_t o[8];
+#pragma unroll
+                        for (int g = 0; g < 8; g++) {
+                            uint32_t x[4];
+#pragma unroll
+                            for (int e = 0; e < 4; e++) {
+                                const uint32_t u = v[4 * g + e] ^ 0x80000000u;                 // product + 2^31, non-negative
+                                const uint32_t t = (u >> 16) * mc.c16 + (u & 0xFFFFu) + mc.adj;  // same class mod m, below 2^24 + 2^16
+                                x[e] = t - __umulhi(t, mc.magic) * mc.m - (uint32_t)mc.half;     // balanced residue
+                            }
+                            o[g] = pack_low_bytes(x[0], x[1], x[2], x[3]);
+                        }
+                        int8_t *dst = reinterpret_cast<int8_t *>(p.C) + (size_t)z * p.plane_c + (size_t)row * p.ldc + col;
+                        // ldc is a multiple of 16 and the planes are padded to it: 16-byte pieces never leave the row
+                        if (col + 16 <= p.ldc) *reinterpret_cast<uint4 *>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
+                        if (col + 32 <= p.ldc) *reinterpret_cast<uint4 *>(dst + 16) = make_uint4(o[4], o[5], o[6], o[7]);
+                    } else {
+                        int32_t *dst = reinterpret_cast<int32_t *>(p.C) + (size_t)z * p.plane_c + (size_t)row * p.ldc + col;
+                        if (col + 32 <= p.N && ((p.ldc | p.plane_c) & 3) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0) {
+#pragma unroll
+                            for (int g = 0; g < 8; g++)
+                                reinterpret_cast<uint4 *>(dst)[g] = make_uint4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 32; e++)
+                                if (col + e < p.N) dst[e] = (int32_t)v[e];
+                        }
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(accempty_bar(acc));
+        }
+    }
+
+    // teardown: everyone meets, then the owning warp releases the tensor memory
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (warp == 1) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
+    }
+    if (threadIdx.x == 0 && abort_flag) atomicExch(p.status, 1);
+}
+
+}  // namespace g8
+
+// ---------------------------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = [] {
+        void *f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+            f = nullptr;
+        return (EncodeTiledFn)f;
+    }();
+    return fn;
+}
+
+// 3-D map {k, row, plane} over K-contiguous int8 planes: row pitch ld bytes (multiple of 16), plane pitch `plane` bytes
+static cudaError_t make_map(CUtensorMap *map, const int8_t *ptr, int K, int rows, int Z, long long ld, size_t plane, int box_rows) {
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return cudaErrorNotSupported;
+    if ((reinterpret_cast<uintptr_t>(ptr) & 15) || (ld & 15) || (plane & 15)) return cudaErrorMisalignedAddress;
+    const cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)Z};
+    const cuuint64_t strides[2] = {(cuuint64_t)ld, (cuuint64_t)plane};
+    const cuuint32_t box[3] = {(cuuint32_t)g8::BKB, (cuuint32_t)box_rows, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<int8_t *>(ptr), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+static cudaError_t gemm_setup() {
+    static cudaError_t once = [] {
+        ModConsts h[MAXM];
+        for (int l = 0; l < MAXM; l++) h[l] = mod_consts(l);
+        cudaError_t e = cudaMemcpyToSymbol(g8::c_modc, h, sizeof h);
+        if (e) return e;
+        e = cudaFuncSetAttribute(g8::gemm_i8_tc<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, g8::SMEM_BYTES);
+        if (e) return e;
+        return cudaFuncSetAttribute(g8::gemm_i8_tc<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, g8::SMEM_BYTES);
+    }();
+    return once;
+}
+
+// C[z] = A[z] * Bt[z]^T for z < Z. A: [Z][M][lda] int8, Bt: [Z][N][ldb] int8 (pitches in bytes, multiples of 16; plane
+// pitches pa, pb). fused = 0: C is int32 [Z][M][ldc]. fused = 1: C is int8 [Z][M][ldc] holding the balanced residue of
+// plane z mod modulus(first_modulus + z); ldc must then be a multiple of 16 with the padding columns writable.
+// `status` is a device int the kernel sets to 1 if a barrier wait expired. `sms` = 0 uses every SM.
+cudaError_t gemm_i8_planes(const int8_t *A, const int8_t *Bt, void *C, int M, int N, int K, int Z, long long lda, long long ldb,
+                           long long ldc, size_t pa, size_t pb, size_t pc, int fused, int first_modulus, int *status, int sms,
+                           cudaStream_t st) {
+    if (M <= 0 || N <= 0 || K <= 0 || Z <= 0) return cudaErrorInvalidValue;
+    if (fused && ((ldc & 15) || first_modulus < 0 || first_modulus + Z > MAXM)) return cudaErrorInvalidValue;
+    cudaError_t e = gemm_setup();
+    if (e) return e;
+    CUtensorMap mapA, mapB;
+    if ((e = make_map(&mapA, A, K, M, Z, lda, pa, g8::BM))) return e;
+    if ((e = make_map(&mapB, Bt, K, N, Z, ldb, pb, g8::BN))) return e;
+    g8::Params p{};
+    p.M = M; p.N = N; p.K = K; p.Z = Z;
+    p.tiles_m = (M + g8::BM - 1) / g8::BM;
+    p.tiles_n = (N + g8::BN - 1) / g8::BN;
+    p.band = 8;
+    p.first_modulus = first_modulus;
+    p.C = C; p.ldc = ldc; p.plane_c = pc; p.status = status;
+    if (sms <= 0) {
+        int dev;
+        if ((e = cudaGetDevice(&dev))) return e;
+        if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev))) return e;
+    }
+    const long long total = (long long)p.tiles_m * p.tiles_n * Z;
+    if (total > 0x7fffffffLL) return cudaErrorInvalidValue;
+    const int grid = (int)(total < sms ? total : sms);
+    if (fused) g8::gemm_i8_tc<true><<<grid, g8::THREADS, g8::SMEM_BYTES, st>>>(mapA, mapB, p);
+    else g8::gemm_i8_tc<false><<<grid, g8::THREADS, g8::SMEM_BYTES, st>>>(mapA, mapB, p);
+    return cudaGetLastError();
+}
+
+}  // namespace ozk

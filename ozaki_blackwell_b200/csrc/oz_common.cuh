@@ -1,0 +1,39 @@
+// oz_common.cuh -- small device helpers shared by the kernels.
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+#include "oz_tables.cuh"
+
+namespace ozk {
+
+__device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c) {   // signed bytes x signed bytes
+    int d;
+    asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {   // unsigned bytes of a x signed bytes of b
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+// byte 0 of four registers into one word
+__device__ __forceinline__ uint32_t pack_low_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
+}
+// u mod m for 0 <= u below the bound checked by magic_ok(): one multiply-high, one multiply-add
+template <int L>
+__device__ __forceinline__ uint32_t mod_magic(uint32_t u) {
+    return u - __umulhi(u, magic_of(L)) * (uint32_t)modulus(L);
+}
+// 2^s as a double for -1022 <= s <= 1023
+__device__ __forceinline__ double pow2_normal(int s) { return __hiloint2double((s + 1023) << 20, 0); }
+// llrint(ldexp(x, s)) as the reference computes it (src/ozaki2.cuh:76). For s in the normal exponent range the scaling
+// is a multiplication by 2^s: exact whenever the result is a normal number, and any result below 2^-1022 rounds to the
+// integer 0 either way. Outside that range (rows whose largest entry is subnormal or above 2^1000) ldexp itself is used.
+__device__ __forceinline__ long long scaled_int(double x, int s, double p2, bool fast) {
+    return __double2ll_rn(fast ? x * p2 : ldexp(x, s));
+}
+// the reference's scale: bits - 1 - ilogb(max |x|), 0 for an all-zero row (src/ozaki2.cuh:66)
+__device__ __forceinline__ int scale_from_max(double mx, int bits) { return mx == 0 ? 0 : bits - 1 - ilogb(mx); }
+
+}  // namespace ozk

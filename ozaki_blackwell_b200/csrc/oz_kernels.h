@@ -1,0 +1,21 @@
+// oz_kernels.h -- host-callable launchers of the four stages (definitions in scale_residue.cu, gemm_i8_sm100.cu, crt.cu)
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace ozk {
+
+cudaError_t scale_residues_rows(int nm, const double *X, int rows, int len, long long ldx, int bits, int *s, int8_t *R, int ld,
+                                size_t plane, cudaStream_t st);
+cudaError_t scale_residues_cols(int nm, const double *X, int rows, int cols, long long ldx, int bits, unsigned long long *colmax,
+                                int *s, int8_t *R, int ld, size_t plane, cudaStream_t st);
+cudaError_t gemm_i8_planes(const int8_t *A, const int8_t *Bt, void *C, int M, int N, int K, int Z, long long lda, long long ldb,
+                           long long ldc, size_t pa, size_t pb, size_t pc, int fused, int first_modulus, int *status, int sms,
+                           cudaStream_t st);
+cudaError_t crt_from_i8(int nm, const int8_t *Cr, size_t plane, int M, int N, long long ldr, const int *sa, const int *sb,
+                        double *C, long long ldc, cudaStream_t st);
+cudaError_t crt_from_i32(int nm, const int32_t *Cl, size_t plane, int M, int N, long long ldr, const int *sa, const int *sb,
+                         double *C, long long ldc, cudaStream_t st);
+
+}  // namespace ozk

@@ -1,0 +1,240 @@
+// scale_residue.cu -- kernels 1 and 2 of the FP64 product: exponent scaling and the int8 residue split.
+//
+// What they compute is the reference's `scales` and `residues<NM>` (src/ozaki2.cuh:56-78):
+//     s[r]       = bits - 1 - ilogb(max_k |X[r,k]|)           (0 for an all-zero row / column)
+//     R[l][r][k] = int8( balanced (llrint(ldexp(X[r,k], s[r])) mod m_l) )    for every modulus l < NM
+// with R stored K-contiguous for both operands (B comes out transposed: Bt[l][j][k]).
+//
+// How: both are HBM-bound, so each input is read as few times as its access pattern allows and the 64-bit "% m" is
+// replaced by byte arithmetic. A row of A is read once: the block keeps it in registers between the max reduction
+// and the residue split. B is scaled per column, which needs a pass over whole columns first (col_absmax, coalesced
+// along rows) and a second, transposing pass. The residue of a 64-bit integer is taken from its eight bytes:
+// v + 2^62 = sum b_i 256^i with b_i unsigned, so v mod m = sum b_i (256^i mod m) - (2^62 mod m): two dp4a per modulus
+// and one multiply-high reduction of a 19-bit sum, instead of a 64-bit division by a constant.
+#include "oz_common.cuh"
+
+namespace ozk {
+
+// ---------------------------------------------------------------------------------------------------------------
+// residues of four consecutive integers for every modulus: calls put(l, word) with the four int8 packed little-endian
+// ---------------------------------------------------------------------------------------------------------------
+template <int NM, class Put>
+__device__ __forceinline__ void residues_of_4(const long long (&v)[4], Put &&put) {
+    uint32_t lo[4], hi[4];
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+        const unsigned long long w = (unsigned long long)v[e] + (1ull << 62);   // |v| < 2^62: w is positive
+        lo[e] = (uint32_t)w;
+        hi[e] = (uint32_t)(w >> 32);
+    }
+    // modulus 256: the balanced residue is the low byte read as int8
+    put(std::integral_constant<int, 0>{}, pack_low_bytes(lo[0], lo[1], lo[2], lo[3]));
+    static_for<1, NM>([&](auto L) {
+        constexpr int l = decltype(L)::value, m = modulus(l);
+        constexpr uint32_t wlo = pack4(byte_weight(0, l), byte_weight(1, l), byte_weight(2, l), byte_weight(3, l));
+        constexpr uint32_t whi = pack4(byte_weight(4, l), byte_weight(5, l), byte_weight(6, l), byte_weight(7, l));
+        constexpr int init = lift_of(l, BYTES_BOUND) - pow2_mod(62, m);
+        static_assert(init > BYTES_BOUND && magic_ok(l, (uint64_t)init + BYTES_BOUND), "multiply-high reduction out of range");
+        uint32_t x[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const uint32_t u = (uint32_t)dp4a_us(hi[e], whi, dp4a_us(lo[e], wlo, init));
+            x[e] = mod_magic<l>(u) - (uint32_t)half_of(l);
+        }
+        put(L, pack_low_bytes(x[0], x[1], x[2], x[3]));
+    });
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// A side: one block per row. R chunks of four doubles per thread stay in registers between the two phases.
+// ---------------------------------------------------------------------------------------------------------------
+template <int NM, int R, int MAXT>
+__global__ void __launch_bounds__(MAXT) row_scale_residues(const double *__restrict__ X, int len, long long ldx, int bits,
+                                                           int *__restrict__ s_out, int8_t *__restrict__ Rp, int ld,
+                                                           size_t plane) {
+    const int r = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
+    const double *row = X + (size_t)r * ldx;
+    const bool vec = ((reinterpret_cast<uintptr_t>(row) & 15) == 0);
+    const int chunks = (len + 3) >> 2;                // chunks of four
+    const bool cached = chunks <= R * nt;             // does the whole row fit the block's registers?
+    double x[R][4];
+    double mx = 0;
+    auto load4 = [&](int c, double (&d)[4]) {
+        const int k = c << 2;
+        if (vec && k + 3 < len) {
+            const double2 a = *reinterpret_cast<const double2 *>(row + k), b = *reinterpret_cast<const double2 *>(row + k + 2);
+            d[0] = a.x; d[1] = a.y; d[2] = b.x; d[3] = b.y;
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; e++) d[e] = k + e < len ? row[k + e] : 0.0;
+        }
+    };
+    if (cached) {
+#pragma unroll
+        for (int i = 0; i < R; i++) {
+            const int c = i * nt + tid;
+            if (c < chunks) load4(c, x[i]);
+            else { x[i][0] = x[i][1] = x[i][2] = x[i][3] = 0.0; }
+#pragma unroll
+            for (int e = 0; e < 4; e++) mx = fmax(mx, fabs(x[i][e]));
+        }
+    } else {
+        for (int c = tid; c < chunks; c += nt) {
+            double d[4];
+            load4(c, d);
+#pragma unroll
+            for (int e = 0; e < 4; e++) mx = fmax(mx, fabs(d[e]));
+        }
+    }
+    // block max: shuffles inside the warp, shared memory across warps
+    __shared__ double wmax[32];
+#pragma unroll
+    for (int o = 16; o; o >>= 1) mx = fmax(mx, __shfl_xor_sync(~0u, mx, o));
+    if ((tid & 31) == 0) wmax[tid >> 5] = mx;
+    __syncthreads();
+    mx = wmax[0];
+    for (int w = 1; w < (nt >> 5); w++) mx = fmax(mx, wmax[w]);
+    const int s = scale_from_max(mx, bits);
+    if (tid == 0) s_out[r] = s;
+
+    const bool fast = s >= -1022 && s <= 1023;
+    const double p2 = pow2_normal(fast ? s : 0);
+    int8_t *out = Rp + (size_t)r * ld;
+    auto emit = [&](int c, const double (&d)[4]) {
+        long long v[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) v[e] = scaled_int(d[e], s, p2, fast);
+        residues_of_4<NM>(v, [&](auto L, uint32_t word) {
+            *reinterpret_cast<uint32_t *>(out + decltype(L)::value * plane + ((size_t)c << 2)) = word;
+        });
+    };
+    if (cached) {
+#pragma unroll
+        for (int i = 0; i < R; i++) {
+            const int c = i * nt + tid;
+            if (c < chunks) emit(c, x[i]);
+        }
+    } else {
+        for (int c = tid; c < chunks; c += nt) {
+            double d[4];
+            load4(c, d);
+            emit(c, d);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// B side, pass 1: per-column max |x| of a row-major K x N matrix, as the bit pattern of a non-negative double
+// (for those the integer order is the numeric order; NaNs are dropped by fmax as in the reference's loop).
+// Block: 256 threads x 2 adjacent columns, ROWS rows; one atomicMax per column per block.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int CM_ROWS = 64;
+__global__ void __launch_bounds__(256) col_absmax(const double *__restrict__ X, int rows, int cols, long long ldx,
+                                                  unsigned long long *__restrict__ colmax) {
+    const int j = (blockIdx.x * 256 + threadIdx.x) * 2;
+    const int k0 = blockIdx.y * CM_ROWS, k1 = min(rows, k0 + CM_ROWS);
+    if (j >= cols) return;
+    const bool pair = j + 1 < cols && ((reinterpret_cast<uintptr_t>(X) & 15) == 0) && (ldx & 1) == 0;
+    double m0 = 0, m1 = 0;
+    if (pair) {
+#pragma unroll 8
+        for (int k = k0; k < k1; k++) {
+            const double2 d = *reinterpret_cast<const double2 *>(X + (size_t)k * ldx + j);
+            m0 = fmax(m0, fabs(d.x));
+            m1 = fmax(m1, fabs(d.y));
+        }
+    } else {
+        for (int k = k0; k < k1; k++) {
+            m0 = fmax(m0, fabs(X[(size_t)k * ldx + j]));
+            if (j + 1 < cols) m1 = fmax(m1, fabs(X[(size_t)k * ldx + j + 1]));
+        }
+    }
+    if (m0 != 0) atomicMax(colmax + j, (unsigned long long)__double_as_longlong(m0));
+    if (j + 1 < cols && m1 != 0) atomicMax(colmax + j + 1, (unsigned long long)__double_as_longlong(m1));
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// B side, pass 2: residues of a row-major K x N matrix written transposed, Rt[l][j][k].
+// Block 256 threads = 8 warps; lane = column, each warp owns 32 consecutive k (two runs of 16), so that reads are
+// 256-byte row segments and every thread writes whole 16-byte pieces of its column's K-contiguous output row.
+// ---------------------------------------------------------------------------------------------------------------
+template <int NM>
+__global__ void __launch_bounds__(256) col_residues_t(const double *__restrict__ X, int rows, int cols, long long ldx,
+                                                      const unsigned long long *__restrict__ colmax, int bits,
+                                                      int *__restrict__ s_out, int8_t *__restrict__ Rp, int ld, size_t plane) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int j = blockIdx.x * 32 + lane;
+    const int kbase = blockIdx.y * 256 + warp * 32;
+    if (j >= cols || kbase >= rows) return;
+    const int s = scale_from_max(__longlong_as_double((long long)colmax[j]), bits);
+    if (blockIdx.y == 0 && warp == 0) s_out[j] = s;
+    const bool fast = s >= -1022 && s <= 1023;
+    const double p2 = pow2_normal(fast ? s : 0);
+    int8_t *out = Rp + (size_t)j * ld;
+#pragma unroll 1
+    for (int half = 0; half < 2; half++) {
+        const int k0 = kbase + half * 16;
+        if (k0 >= rows) break;
+        double d[16];
+#pragma unroll
+        for (int e = 0; e < 16; e++) d[e] = k0 + e < rows ? X[(size_t)(k0 + e) * ldx + j] : 0.0;
+        uint32_t w[NM][4];
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            long long v[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) v[e] = scaled_int(d[4 * q + e], s, p2, fast);
+            residues_of_4<NM>(v, [&](auto L, uint32_t word) { w[decltype(L)::value][q] = word; });
+        }
+#pragma unroll
+        for (int l = 0; l < NM; l++)
+            *reinterpret_cast<uint4 *>(out + l * plane + k0) = make_uint4(w[l][0], w[l][1], w[l][2], w[l][3]);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// launchers (nm is a run-time value in the API, a template parameter in the kernels)
+// ---------------------------------------------------------------------------------------------------------------
+template <int NM>
+static cudaError_t launch_rows_t(const double *X, int rows, int len, long long ldx, int bits, int *s, int8_t *R, int ld,
+                                 size_t plane, cudaStream_t st) {
+    constexpr int RR = 8, MAXT = 512;           // 64 registers of row data per thread, 128 allowed
+    int nt = ((len + 3) / 4 + RR - 1) / RR;     // threads that hold the row in registers
+    nt = (nt + 31) / 32 * 32;
+    if (nt < 32) nt = 32;
+    if (nt > MAXT) nt = MAXT;                   // longer rows (K > 16384) are read twice; the second read mostly hits L2
+    row_scale_residues<NM, RR, MAXT><<<rows, nt, 0, st>>>(X, len, ldx, bits, s, R, ld, plane);
+    return cudaGetLastError();
+}
+template <int NM>
+static cudaError_t launch_cols_t(const double *X, int rows, int cols, long long ldx, int bits, unsigned long long *colmax,
+                                 int *s, int8_t *R, int ld, size_t plane, cudaStream_t st) {
+    cudaError_t e = cudaMemsetAsync(colmax, 0, (size_t)cols * 8, st);
+    if (e) return e;
+    col_absmax<<<dim3((cols + 511) / 512, (rows + CM_ROWS - 1) / CM_ROWS), 256, 0, st>>>(X, rows, cols, ldx, colmax);
+    col_residues_t<NM><<<dim3((cols + 31) / 32, (rows + 255) / 256), 256, 0, st>>>(X, rows, cols, ldx, colmax, bits, s, R, ld, plane);
+    return cudaGetLastError();
+}
+
+#define OZ_DISPATCH_NM(nm, CALL)                                                                                  \
+    switch (nm) {                                                                                                 \
+    case 8: { constexpr int NM = 8; return CALL; }    case 9: { constexpr int NM = 9; return CALL; }              \
+    case 10: { constexpr int NM = 10; return CALL; }  case 11: { constexpr int NM = 11; return CALL; }            \
+    case 12: { constexpr int NM = 12; return CALL; }  case 13: { constexpr int NM = 13; return CALL; }            \
+    case 14: { constexpr int NM = 14; return CALL; }  case 15: { constexpr int NM = 15; return CALL; }            \
+    case 16: { constexpr int NM = 16; return CALL; }                                                              \
+    default: return cudaErrorInvalidValue;                                                                        \
+    }
+
+// A-like operand: `rows` rows of `len` contiguous doubles, row pitch ldx; writes s[rows] and R[nm][rows][ld]
+cudaError_t scale_residues_rows(int nm, const double *X, int rows, int len, long long ldx, int bits, int *s, int8_t *R, int ld,
+                                size_t plane, cudaStream_t st) {
+    OZ_DISPATCH_NM(nm, (launch_rows_t<NM>(X, rows, len, ldx, bits, s, R, ld, plane, st)));
+}
+// B-like operand: row-major `rows` x `cols` (rows = K), scaled per column; writes s[cols] and Rt[nm][cols][ld]
+cudaError_t scale_residues_cols(int nm, const double *X, int rows, int cols, long long ldx, int bits, unsigned long long *colmax,
+                                int *s, int8_t *R, int ld, size_t plane, cudaStream_t st) {
+    OZ_DISPATCH_NM(nm, (launch_cols_t<NM>(X, rows, cols, ldx, bits, colmax, s, R, ld, plane, st)));
+}
+
+}  // namespace ozk

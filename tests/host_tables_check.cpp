@@ -1,0 +1,115 @@
+// host_tables_check.cpp -- CPU check of the integer identities the device kernels rely on (compiled and run by
+// tests/test_host_tables.py with g++; no GPU involved). Uses the same constexpr tables as the kernels
+// (ozaki_blackwell_b200/csrc/oz_tables.cuh) and emulates dp4a / umulhi in plain C++.
+//   1. residues of a 64-bit integer from its bytes          (scale_residue.cu: residues_of_4)
+//   2. balanced residue of an int32 product by 16-bit split  (gemm_i8_sm100.cu: fused epilogue)
+//   3. Garner digits with one reduction per digit            (crt.cu: garner_horner)
+// Each is compared with the reference's definition: bal(x, m) and the step-by-step Garner recurrence
+// (src/ozaki2.cuh:38-42, 86-92 of the reference).
+#include <cstdint>
+#include <cstdio>
+#include <random>
+#include "oz_tables.cuh"
+using namespace ozk;
+
+static int dp4a(uint32_t a, uint32_t b, int c, bool a_signed) {
+    for (int i = 0; i < 4; i++) {
+        const int x = a_signed ? (int)(int8_t)(a >> (8 * i)) : (int)(uint8_t)(a >> (8 * i));
+        c += x * (int)(int8_t)(b >> (8 * i));
+    }
+    return c;
+}
+static uint32_t umulhi(uint32_t a, uint32_t b) { return (uint32_t)(((uint64_t)a * b) >> 32); }
+static int bal(long long x, int m) { return bal_c(x, m); }
+
+template <int L> struct PerMod {
+    static int residue_from_bytes(long long v) {
+        constexpr int l = L, m = modulus(l);
+        if (l == 0) return (int)(int8_t)(v & 255);
+        constexpr uint32_t wlo = pack4(byte_weight(0, l), byte_weight(1, l), byte_weight(2, l), byte_weight(3, l));
+        constexpr uint32_t whi = pack4(byte_weight(4, l), byte_weight(5, l), byte_weight(6, l), byte_weight(7, l));
+        constexpr int init = lift_of(l, BYTES_BOUND) - pow2_mod(62, m);
+        static_assert(init > BYTES_BOUND && magic_ok(l, (uint64_t)init + BYTES_BOUND), "range");
+        const uint64_t w = (uint64_t)v + (1ull << 62);
+        const uint32_t u = (uint32_t)dp4a((uint32_t)(w >> 32), whi, dp4a((uint32_t)w, wlo, init, false), false);
+        return (int)(int8_t)((u - umulhi(u, magic_of(l)) * (uint32_t)m - (uint32_t)half_of(l)) & 255);
+    }
+    static int residue_of_product(int32_t x) {
+        constexpr ModConsts mc = mod_consts(L);
+        const uint32_t u = (uint32_t)x ^ 0x80000000u;
+        const uint32_t t = (u >> 16) * mc.c16 + (u & 0xFFFFu) + mc.adj;
+        return (int)(int8_t)((t - umulhi(t, mc.magic) * mc.m - (uint32_t)mc.half) & 255);
+    }
+};
+
+template <int NM> static void garner_fast(const int *r, int *x) {   // r: balanced residues
+    uint32_t X[(NM + 3) / 4] = {};
+    for (int l = 0; l < NM; l++) X[l / 4] |= (uint32_t)(r[l] & 255) << (8 * (l % 4));
+    x[0] = (int)(int8_t)(X[0] & 255);
+    static_for<1, NM>([&](auto Lc) {
+        constexpr int l = decltype(Lc)::value, m = modulus(l);
+        int acc = lift_of(l, GARNER_BOUND);
+        for (int g = 0; g <= l / 4; g++) {
+            int c[4];
+            for (int q = 0; q < 4; q++) { const int idx = 4 * g + q; c[q] = idx < l ? garner_q(idx, l) : (idx == l ? garner_p(l) : 0); }
+            acc = dp4a(X[g], pack4(c[0], c[1], c[2], c[3]), acc, true);
+        }
+        const uint32_t rr = (uint32_t)acc - umulhi((uint32_t)acc, magic_of(l)) * (uint32_t)m;
+        const int xl = (int)rr - half_of(l);
+        X[l / 4] = (X[l / 4] & ~(255u << (8 * (l % 4)))) | ((uint32_t)(xl & 255) << (8 * (l % 4)));
+        x[l] = xl;
+    });
+}
+template <int NM> static void garner_ref(const int *r, int *x) {   // src/ozaki2.cuh:86-92
+    for (int l = 0; l < NM; l++) {
+        const int m = modulus(l);
+        int v = bal(r[l], m);
+        for (int t = 0; t < l; t++) v = bal((long long)(v - x[t]) * garner_inv(t, l), m);
+        x[l] = v;
+    }
+}
+
+template <int L> static long check_mod(std::mt19937_64 &g) {
+    long bad = 0;
+    constexpr int m = modulus(L);
+    const long long edge[] = {0, 1, -1, 127, 128, -128, -129, 255, 256, (1ll << 61), -(1ll << 61), (1ll << 62) - 1, -(1ll << 62) + 1,
+                              (1ll << 57) - 1, -(1ll << 57)};
+    for (long long v : edge) bad += PerMod<L>::residue_from_bytes(v) != bal(v, m);
+    for (int i = 0; i < 50000; i++) {
+        const long long v = (long long)(g() >> 1) - (1ll << 62);
+        bad += PerMod<L>::residue_from_bytes(v) != bal(v, m);
+        const long long small = (long long)(g() % 100001) - 50000;
+        bad += PerMod<L>::residue_from_bytes(small) != bal(small, m);
+    }
+    const int32_t pedge[] = {0, 1, -1, INT32_MAX, INT32_MIN, INT32_MIN + 1, 65535, 65536, -65536, -65537, 128 * 128 * 131071, -128 * 127 * 131071};
+    for (int32_t x : pedge) bad += PerMod<L>::residue_of_product(x) != bal(x, m);
+    for (int i = 0; i < 100000; i++) { const int32_t x = (int32_t)g(); bad += PerMod<L>::residue_of_product(x) != bal(x, m); }
+    // every value of the high half with the extreme low halves (the bound of the multiply-high is tight for m = 255)
+    for (uint32_t hi = 0; hi < 65536; hi++)
+        for (uint32_t lo : {0u, 1u, 65534u, 65535u}) { const int32_t x = (int32_t)((hi << 16) | lo); bad += PerMod<L>::residue_of_product(x) != bal(x, m); }
+    return bad;
+}
+template <int NM> static long check_garner(std::mt19937_64 &g) {
+    long bad = 0;
+    for (int i = 0; i < 6000; i++) {
+        int r[NM], a[NM], b[NM];
+        for (int l = 0; l < NM; l++) {
+            const int m = modulus(l);
+            r[l] = i < 4 ? (i == 0 ? -(m / 2) : i == 1 ? (m + 1) / 2 - 1 : i == 2 ? 0 : ((l & 1) ? -(m / 2) : (m + 1) / 2 - 1))
+                         : bal((long long)(g() % m), m);
+        }
+        garner_fast<NM>(r, a);
+        garner_ref<NM>(r, b);
+        for (int l = 0; l < NM; l++) bad += a[l] != b[l];
+    }
+    return bad;
+}
+
+int main() {
+    std::mt19937_64 g(12345);
+    long bad = 0;
+    static_for<0, MAXM>([&](auto L) { bad += check_mod<decltype(L)::value>(g); });
+    static_for<8, 17>([&](auto N) { bad += check_garner<decltype(N)::value>(g); });
+    printf("%ld wrong\n", bad);
+    return bad != 0;
+}

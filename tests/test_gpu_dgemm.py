@@ -1,0 +1,131 @@
+"""The whole product through the reference's entry point ozb_dgemm, bit for bit against the CPU checker, and the
+reference's own accuracy cases (GPU tests)."""
+import ctypes
+
+import numpy as np
+import pytest
+
+import oracle_lib as o
+
+pytestmark = pytest.mark.gpu
+
+
+def _gu():
+    import gpu_util
+    return gpu_util
+
+
+@pytest.mark.parametrize("nm", list(range(8, 17)))
+def test_config1_bit_exact_all_modulus_counts(nm):
+    """M = N = 256, K = 512, entries U[-1,1) * 2^e, e in [-8, 8], seed 0."""
+    g = _gu()
+    A, B = g.synthetic(256, 512, 0), g.synthetic(512, 256, 1)
+    got = g.gpu_dgemm(A, B, nm)
+    want = o.dgemm(A, B, nm)
+    assert g.same_bits(got, want), g.describe_mismatch(got, want)
+    if nm == 16:
+        assert o.err_units(A, B, got) <= 2.0
+
+
+@pytest.mark.parametrize("shape", [(200, 300, 500), (1, 1, 1), (3, 5, 7), (129, 257, 129), (257, 100, 2049), (64, 1000, 33)])
+def test_odd_shapes_bit_exact(shape):
+    g = _gu()
+    M, N, K = shape
+    A, B = g.synthetic(M, K, 5), g.synthetic(K, N, 6)
+    got = g.gpu_dgemm(A, B, 16)
+    want = o.dgemm(A, B, 16)
+    assert g.same_bits(got, want), g.describe_mismatch(got, want)
+
+
+def test_host_operands_match_device_operands():
+    g = _gu()
+    A, B = g.synthetic(130, 700, 7), g.synthetic(700, 90, 8)
+    assert g.same_bits(g.gpu_dgemm(A, B, 14, on_host=True), g.gpu_dgemm(A, B, 14, on_host=False))
+    assert g.same_bits(g.gpu_dgemm(A, B, 14, on_host=True), o.dgemm(A, B, 14))
+
+
+@pytest.mark.parametrize("case", [(512, 0, 0.99), (512, 8, 3.1), (4096, 0, 0.24), (4096, 8, 1.87), (4096, 16, 4.7), (4096, 32, 31.5)])
+def test_reference_accuracy_cases(case):
+    """The reference's accuracy table (bench/ozaki_test.cu:36-41, README.md:47-52,259) at 16 moduli: same inputs, same
+    error, and the same bits as the CPU checker."""
+    g = _gu()
+    K, spread, published = case
+    A = o.ref_fill(256 * K, spread, 1 + K).reshape(256, K)
+    B = o.ref_fill(K * 256, spread, 2 + K).reshape(K, 256)
+    got = g.gpu_dgemm(A, B, 16)
+    assert g.same_bits(got, o.dgemm(A, B, 16))
+    err = o.err_units(A, B, got)
+    assert abs(err - published) <= 0.02 * published + 0.006, (err, published)
+
+
+def test_zero_rows_columns_and_special_magnitudes():
+    g = _gu()
+    M, N, K = 140, 270, 300
+    A, B = g.synthetic(M, K, 9), g.synthetic(K, N, 10)
+    A[3, :] = 0
+    B[:, 5] = 0
+    A[4, :] *= 2.0 ** 600
+    B[:, 6] *= 2.0 ** -700
+    A[5, :] = np.ldexp(A[5, :], -1040)      # subnormal row
+    got = g.gpu_dgemm(A, B, 16)
+    want = o.dgemm(A, B, 16)
+    assert g.same_bits(got, want), g.describe_mismatch(got, want)
+    assert np.all(got[3] == 0) and np.all(got[:, 5] == 0)
+
+
+def test_argument_errors_match_the_reference():
+    """python/capi.cu:23-29,79: non-positive sizes and moduli outside 8..16 -> 10001, K >= 131072 -> 10002."""
+    from ozaki_blackwell_b200._lib import lib
+    z = ctypes.c_void_p(0)
+    assert lib.ozb_dgemm(0, 4, 4, z, z, z, 16, 0) == 10001
+    assert lib.ozb_dgemm(4, 4, -1, z, z, z, 16, 0) == 10001
+    assert lib.ozb_dgemm(4, 4, 4, z, z, z, 7, 0) == 10001
+    assert lib.ozb_dgemm(4, 4, 4, z, z, z, 17, 0) == 10001
+    assert lib.ozb_dgemm(4, 4, 131072, z, z, z, 16, 0) == 10002
+    assert lib.ozb_tdgemm(4, 4, 4, *([z] * 9), 0) == 10005
+    assert lib.ozb_error(0) == b"ok"
+
+
+def test_python_wrapper_numpy_and_torch():
+    import torch
+    import ozaki_blackwell_b200 as ob
+    g = _gu()
+    A, B = g.synthetic(96, 200, 12), g.synthetic(200, 64, 13)
+    want = o.dgemm(A, B, 16)
+    assert g.same_bits(ob.matmul(A, B), want)
+    Ct = ob.matmul(torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda())
+    assert g.same_bits(Ct.cpu().numpy(), want)
+    out = np.empty((96, 64))
+    assert ob.matmul(A, B, moduli=12, out=out) is out and g.same_bits(out, o.dgemm(A, B, 12))
+    info = ob.device()
+    assert info["sm"] // 10 == 10 and info["sms"] > 0
+    with pytest.raises(ob.OzakiError):
+        ob.matmul(A, B, moduli=3)
+    ob.release()
+
+
+def test_plan_reuse_and_row_block_sharding_is_bit_identical():
+    """Row blocks of A give the same rows of C (the scales of A are per row, those of B per column of the whole B):
+    the property the multi-GPU partition rests on."""
+    g = _gu()
+    M, N, K = 512, 384, 640
+    A, B = g.synthetic(M, K, 14), g.synthetic(K, N, 15)
+    full = g.gpu_dgemm(A, B, 16)
+    for parts in (2, 4):
+        rows = M // parts
+        got = np.vstack([g.gpu_dgemm(A[r * rows:(r + 1) * rows], B, 16) for r in range(parts)])
+        assert g.same_bits(got, full)
+
+
+def test_medium_size_sampled_against_checker_rows():
+    """n = 2048: too large for the full CPU product in a test, so the checker recomputes a band of rows (row blocks are
+    independent) and the error is measured on a sample."""
+    g = _gu()
+    n = 2048
+    A, B = g.synthetic(n, n, 16), g.synthetic(n, n, 17)
+    got = g.gpu_dgemm(A, B, 16)
+    rows = slice(1000, 1032)
+    want = o.dgemm(A[rows], B, 16)
+    assert g.same_bits(got[rows], want), g.describe_mismatch(got[rows], want)
+    idx = np.random.default_rng(1).integers(0, n * n, 512)
+    assert o.err_units_sampled(A, B, got, idx) <= 2.0
