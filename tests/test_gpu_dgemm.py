@@ -24,7 +24,10 @@ def test_config1_bit_exact_all_modulus_counts(nm):
     want = o.dgemm(A, B, nm)
     assert g.same_bits(got, want), g.describe_mismatch(got, want)
     if nm == 16:
-        assert o.err_units(A, B, got) <= 2.0
+        # K = 512 is the hard case of this family (the reference publishes 3.1 units for its own K = 512, 2^+-8 inputs,
+        # README.md:49); the bound asserted here is the reference's own self-test threshold, 8 units
+        # (python/ozaki_blackwell/__main__.py:38-44). The bits are the checker's, so the value is the algorithm's.
+        assert o.err_units(A, B, got) <= 8.0
 
 
 @pytest.mark.parametrize("shape", [(200, 300, 500), (1, 1, 1), (3, 5, 7), (129, 257, 129), (257, 100, 2049), (64, 1000, 33)])
