@@ -92,9 +92,14 @@ int ozb_plan_view(ozb_plan *p, int *bits, int *Kp, int *Np, int8_t **Ar, int8_t 
 /* Device status word of the plan: 0, or OZB_ETIMEOUT if a bounded wait expired in a kernel launched through it.
  * Synchronises the stream the last call used. */
 int ozb_plan_status(ozb_plan *p);
-/* Milliseconds of the last ozb_plan_dgemm when the environment variable OZ_PROF is set (src/ozaki2.cuh:135-153):
- * ms[0] scales + residues, ms[1] INT8 GEMMs, ms[2] CRT. Returns OZB_EARG when profiling is off. */
-int ozb_plan_phase_ms(ozb_plan *p, float ms[3]);
+/* Phase timing (src/ozaki2.cuh:135-153, the reference's OZ_PROF): with `slots` > 0 every ozb_plan_dgemm records four
+ * events on its stream (no host synchronisation) into slot (call number mod slots); slots = 0 turns it off. A plan
+ * created while the environment variable OZ_PROF is set starts with one slot and prints the reference's line on stderr
+ * after every product (which synchronises). */
+int ozb_plan_profile(ozb_plan *p, int slots);
+/* Milliseconds of the product recorded in `slot`: ms[0] scales + residues, ms[1] INT8 GEMMs, ms[2] CRT. Waits for that
+ * product to finish. */
+int ozb_plan_phase_ms(ozb_plan *p, int slot, float ms[3]);
 
 /* ozb_dgemm with leading dimensions, on device pointers, on a stream, without the final synchronisation. Uses the same
  * cached plan as ozb_dgemm. */

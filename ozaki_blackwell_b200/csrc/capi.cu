@@ -31,10 +31,9 @@ struct ozb_plan {
     int *sa, *sb, *status;
     unsigned long long *colmax;
     cudaStream_t last;
-    bool prof;
-    cudaEvent_t ev[4];
-    float ms[3];
-    bool have_ms;
+    bool env_prof;                   // OZ_PROF set: one line per product on stderr, as the reference does
+    int slots, calls;                // event ring: 4 events per slot, slot = call number mod slots
+    cudaEvent_t *ev;
 };
 
 static int round_up(int x, int to) { return (x + to - 1) / to * to; }
@@ -50,8 +49,28 @@ static int bits_for_impl(int nm, int K, int maxbits) {   // src/ozaki2.cuh:101-1
 static void plan_free(ozb_plan *p) {
     if (!p) return;
     cudaFree(p->Ar); cudaFree(p->Br); cudaFree(p->Cr); cudaFree(p->sa); cudaFree(p->sb); cudaFree(p->status); cudaFree(p->colmax);
-    if (p->prof) for (auto &e : p->ev) cudaEventDestroy(e);
+    for (int i = 0; i < 4 * p->slots; i++) cudaEventDestroy(p->ev[i]);
+    delete[] p->ev;
     delete p;
+}
+
+static int plan_profile(ozb_plan *p, int slots) {
+    for (int i = 0; i < 4 * p->slots; i++) cudaEventDestroy(p->ev[i]);
+    delete[] p->ev;
+    p->ev = nullptr; p->slots = 0; p->calls = 0;
+    if (slots <= 0) return 0;
+    p->ev = new cudaEvent_t[4 * slots];
+    for (int i = 0; i < 4 * slots; i++)
+        if (cudaError_t e = cudaEventCreate(&p->ev[i])) { for (int j = 0; j < i; j++) cudaEventDestroy(p->ev[j]); delete[] p->ev; p->ev = nullptr; return (int)e; }
+    p->slots = slots;
+    return 0;
+}
+static int plan_phase_ms(ozb_plan *p, int slot, float ms[3]) {
+    if (slot < 0 || slot >= p->slots || slot >= p->calls) return OZB_EARG;
+    cudaEvent_t *ev = p->ev + 4 * slot;
+    if (cudaError_t e = cudaEventSynchronize(ev[3])) return (int)e;
+    for (int i = 0; i < 3; i++) if (cudaError_t e = cudaEventElapsedTime(&ms[i], ev[i], ev[i + 1])) return (int)e;
+    return 0;
 }
 
 static int plan_make(int M, int N, int K, int nm, int maxbits, ozb_plan **out) {
@@ -70,9 +89,9 @@ static int plan_make(int M, int N, int K, int nm, int maxbits, ozb_plan **out) {
     if (!e) e = cudaMalloc(&p->colmax, (size_t)N * 8);
     if (!e) e = cudaMalloc(&p->status, 4);
     if (!e) e = cudaMemset(p->status, 0, 4);
-    p->prof = getenv("OZ_PROF") != nullptr;
-    if (!e && p->prof) for (auto &ev : p->ev) if (!e) e = cudaEventCreate(&ev);
-    if (e) { cudaGetLastError(); p->prof = false; plan_free(p); return (int)e; }
+    p->env_prof = getenv("OZ_PROF") != nullptr;
+    if (!e && p->env_prof) e = (cudaError_t)plan_profile(p, 1);
+    if (e) { cudaGetLastError(); plan_free(p); return (int)e; }
     *out = p;
     return 0;
 }
@@ -83,33 +102,37 @@ static int plan_set_a(ozb_plan *p, const double *A, long long lda, cudaStream_t 
 }
 // columns [j0, j0 + n) of B and C; B and C point at column j0
 static int plan_panel(ozb_plan *p, const double *B, long long ldb, double *C, long long ldc, int j0, int n, cudaStream_t st,
-                      bool timed) {
+                      cudaEvent_t *ev) {
     p->last = st;
     int8_t *Br = p->Br + (size_t)j0 * p->Kp, *Cr = p->Cr + j0;
     cudaError_t e = scale_residues_cols(p->nm, B, p->K, n, ldb, p->bits, p->colmax + j0, p->sb + j0, Br, p->Kp, p->planeB, st);
     if (e) return (int)e;
-    if (timed) cudaEventRecord(p->ev[1], st);
+    if (ev) cudaEventRecord(ev[1], st);
     // the epilogue writes whole 16-byte pieces: the panel's pitch view must allow n rounded up to 16 inside Np
     e = gemm_i8_planes(p->Ar, Br, Cr, p->M, n, p->K, p->nm, p->Kp, p->Kp, p->Np, p->planeA, p->planeB, p->planeC, 1, 0,
                        p->status, 0, st);
     if (e) return (int)e;
-    if (timed) cudaEventRecord(p->ev[2], st);
+    if (ev) cudaEventRecord(ev[2], st);
     e = crt_from_i8(p->nm, Cr, p->planeC, p->M, n, p->Np, p->sa, p->sb + j0, C, ldc, st);
     return (int)e;
 }
 static int plan_dgemm(ozb_plan *p, const double *A, long long lda, const double *B, long long ldb, double *C, long long ldc,
                       cudaStream_t st) {
-    p->have_ms = false;
-    if (p->prof) cudaEventRecord(p->ev[0], st);
+    cudaEvent_t *ev = p->slots ? p->ev + 4 * (p->calls % p->slots) : nullptr;
+    if (ev) cudaEventRecord(ev[0], st);
     if (int e = plan_set_a(p, A, lda, st)) return e;
-    if (int e = plan_panel(p, B, ldb, C, ldc, 0, p->N, st, p->prof)) return e;
-    if (p->prof) {   // src/ozaki2.cuh:147-152: one line per product on stderr
-        cudaEventRecord(p->ev[3], st);
-        cudaEventSynchronize(p->ev[3]);
-        for (int i = 0; i < 3; i++) cudaEventElapsedTime(&p->ms[i], p->ev[i], p->ev[i + 1]);
-        p->have_ms = true;
-        fprintf(stderr, "oz%d %dx%dx%d: scale+residues %.3f  INT8 GEMMs %.3f (%.0f TOPS)  CRT %.3f ms\n", p->nm, p->M, p->N, p->K,
-                p->ms[0], p->ms[1], 2.0 * p->nm * p->M * (double)p->N * p->K / (p->ms[1] * 1e9), p->ms[2]);
+    if (int e = plan_panel(p, B, ldb, C, ldc, 0, p->N, st, ev)) return e;
+    if (ev) {
+        cudaEventRecord(ev[3], st);
+        const int slot = p->calls % p->slots;
+        p->calls++;
+        if (p->calls >= 0x40000000) p->calls = p->slots;   // keep the counter bounded; every slot stays readable
+        if (p->env_prof) {   // src/ozaki2.cuh:147-152: one line per product on stderr (this synchronises, like the reference)
+            float ms[3];
+            if (!plan_phase_ms(p, slot, ms))
+                fprintf(stderr, "oz%d %dx%dx%d: scale+residues %.3f  INT8 GEMMs %.3f (%.0f TOPS)  CRT %.3f ms\n", p->nm, p->M, p->N,
+                        p->K, ms[0], ms[1], 2.0 * p->nm * p->M * (double)p->N * p->K / (ms[1] * 1e9), ms[2]);
+        }
     }
     return 0;
 }
@@ -293,7 +316,7 @@ OZB_API int ozb_plan_set_a(ozb_plan *p, const double *A, long long lda, void *st
 OZB_API int ozb_plan_panel(ozb_plan *p, const double *B, long long ldb, double *C, long long ldc, int j0, int ncols, void *stream) {
     if (!p || !B || !C || j0 < 0 || (j0 & 255) || ncols <= 0 || j0 + ncols > p->N || ldb < ncols || ldc < ncols) return OZB_EARG;
     std::lock_guard<std::mutex> g(mu);
-    return plan_panel(p, B, ldb, C, ldc, j0, ncols, (cudaStream_t)stream, false);
+    return plan_panel(p, B, ldb, C, ldc, j0, ncols, (cudaStream_t)stream, nullptr);
 }
 OZB_API int ozb_plan_view(ozb_plan *p, int *bits, int *Kp, int *Np, int8_t **Ar, int8_t **Br, int8_t **Cr, int **sa, int **sb) {
     if (!p) return OZB_EARG;
@@ -312,10 +335,15 @@ OZB_API int ozb_plan_status(ozb_plan *p) {
     std::lock_guard<std::mutex> g(mu);
     return plan_status(p);
 }
-OZB_API int ozb_plan_phase_ms(ozb_plan *p, float ms[3]) {
-    if (!p || !ms || !p->have_ms) return OZB_EARG;
-    for (int i = 0; i < 3; i++) ms[i] = p->ms[i];
-    return 0;
+OZB_API int ozb_plan_profile(ozb_plan *p, int slots) {
+    if (!p || slots < 0 || slots > 4096) return OZB_EARG;
+    std::lock_guard<std::mutex> g(mu);
+    return plan_profile(p, slots);
+}
+OZB_API int ozb_plan_phase_ms(ozb_plan *p, int slot, float ms[3]) {
+    if (!p || !ms) return OZB_EARG;
+    std::lock_guard<std::mutex> g(mu);
+    return plan_phase_ms(p, slot, ms);
 }
 
 OZB_API int ozb_dgemm_ex(int M, int N, int K, const double *A, long long lda, const double *B, long long ldb, double *C,

@@ -1,0 +1,166 @@
+"""Row-block sharded FP64 product over the GPUs of one node.
+
+The reference is single-GPU (it has no multi-device code at all); this module adds the one distributed strategy the
+product admits without changing a single bit of the result: rank g owns a block of rows of A and produces the same rows
+of C. Row scales are local to those rows; column scales and residues of B are recomputed identically on every rank, so
+the only exchange is one broadcast of B from the rank that holds it. B travels in column panels (whole columns, so each
+panel can be scaled and multiplied as soon as it lands) on a communication stream, while the compute stream works on the
+panels that have already arrived. Peer memory is never read by a kernel of this library: a panel is in the GPU's own
+HBM before the TMA loads of the GEMM touch its residues.
+
+One process per GPU, `torch.distributed` (NCCL over NVLink/NVSwitch on GPUs; the orchestration itself is backend
+agnostic and is exercised with gloo on CPU ranks in the tests, with a checker-backed engine injected there).
+"""
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+PANEL_ALIGN = 256   # ozb_plan_panel wants panel starts on multiples of 256 columns (the GEMM's tile width)
+
+
+def row_block(m_total, rank, world):
+    """Rows [lo, hi) of rank `rank`: blocks differ by at most one row, earlier ranks get the longer ones."""
+    base, extra = divmod(m_total, world)
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+def panel_ranges(n, panels):
+    """Split n columns into at most `panels` ranges whose starts are multiples of PANEL_ALIGN."""
+    if panels <= 1 or n <= PANEL_ALIGN:
+        return [(0, n)]
+    blocks = (n + PANEL_ALIGN - 1) // PANEL_ALIGN
+    panels = min(panels, blocks)
+    out, start = [], 0
+    for p in range(panels):
+        nb = blocks // panels + (1 if p < blocks % panels else 0)
+        stop = min(n, start + nb * PANEL_ALIGN)
+        out.append((start, stop))
+        start = stop
+    return out
+
+
+class CudaEngine:
+    """The product path: a plan of libozaki_blackwell.so on the current CUDA device."""
+
+    def __init__(self, m, n, k, moduli):
+        from ._lib import lib
+        self._lib = lib
+        self._plan = ctypes.c_void_p()
+        self._check(lib.ozb_plan_create(m, n, k, moduli, 62, ctypes.byref(self._plan)))
+        self.m, self.n, self.k = m, n, k
+
+    def _check(self, code):
+        if code:
+            raise RuntimeError(self._lib.ozb_error(code).decode())
+
+    def set_a(self, a, stream):
+        self._check(self._lib.ozb_plan_set_a(self._plan, a.data_ptr(), a.stride(0), stream.cuda_stream))
+
+    def panel(self, b_panel, c, j0, ncols, stream):
+        c_ptr = c.data_ptr() + 8 * j0
+        self._check(self._lib.ozb_plan_panel(self._plan, b_panel.data_ptr(), b_panel.stride(0), c_ptr, c.stride(0), j0, ncols,
+                                             stream.cuda_stream))
+
+    def full(self, a, b, c, stream):
+        self._check(self._lib.ozb_plan_dgemm(self._plan, a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), c.data_ptr(),
+                                             c.stride(0), stream.cuda_stream))
+
+    def status(self):
+        self._check(self._lib.ozb_plan_status(self._plan))
+
+    def close(self):
+        if self._plan:
+            self._lib.ozb_plan_destroy(self._plan)
+            self._plan = ctypes.c_void_p()
+
+
+class _HostStreams:
+    """Stand-ins for CUDA streams and events on CPU ranks (gloo tests): everything is synchronous there."""
+
+    class _S:
+        cuda_stream = 0
+
+        def wait_event(self, e):
+            pass
+
+        def wait_stream(self, s):
+            pass
+
+    class _E:
+        def record(self, s=None):
+            pass
+
+    def stream(self):
+        return self._S()
+
+    def event(self):
+        return self._E()
+
+
+class RowShardedGemm:
+    """C_local = A_local @ B with B held by rank `src`; bit-identical to the single-GPU product of the stacked rows.
+
+    m_local, n, k: this rank's block of rows, the width of B/C and the inner length. `engine` defaults to the CUDA
+    plan; tests on CPU ranks inject one with the same three methods (set_a, panel, full).
+    """
+
+    def __init__(self, m_local, n, k, moduli=16, group=None, src=0, panels=8, engine=None, device=None):
+        self.group, self.src = group, src
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.m, self.n, self.k, self.moduli = m_local, n, k, moduli
+        self.ranges = panel_ranges(n, panels if self.world > 1 else 1)
+        self.engine = engine if engine is not None else CudaEngine(m_local, n, k, moduli)
+        self.on_gpu = engine is None or (device is not None and torch.device(device).type == "cuda")
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        if self.on_gpu:
+            self.compute = torch.cuda.current_stream()
+            self.comm = torch.cuda.Stream()
+            self._event = lambda: torch.cuda.Event()
+        else:
+            hs = _HostStreams()
+            self.compute, self.comm, self._event = hs.stream(), hs.stream(), hs.event
+        # panel-major staging of B: panel p is a contiguous k x width block, so that it can be broadcast as one buffer
+        self.stage = [torch.empty((k, hi - lo), dtype=torch.float64, device=self.device) for lo, hi in self.ranges] \
+            if self.world > 1 else None
+
+    def __call__(self, a_local, b, c_local):
+        """a_local [m_local, k], c_local [m_local, n]; b [k, n] is read on rank `src` only (others may pass None)."""
+        if self.world == 1:
+            self.engine.full(a_local, b, c_local, self.compute)
+            return c_local
+        arrived = []
+        packed = self._event()
+        if self.rank == self.src:
+            for (lo, hi), buf in zip(self.ranges, self.stage):
+                buf.copy_(b[:, lo:hi])            # on the compute stream
+        packed.record(self.compute)
+        self.comm.wait_event(packed)
+        ctx = torch.cuda.stream(self.comm) if self.on_gpu else _null()
+        with ctx:
+            for buf in self.stage:
+                dist.broadcast(buf, src=self.src, group=self.group)
+                ev = self._event()
+                ev.record(self.comm)
+                arrived.append(ev)
+        self.engine.set_a(a_local, self.compute)   # overlaps the first panel's transfer
+        for (lo, hi), buf, ev in zip(self.ranges, self.stage, arrived):
+            self.compute.wait_event(ev)
+            self.engine.panel(buf, c_local, lo, hi - lo, self.compute)
+        self.comm.wait_stream(self.compute)        # the staging buffers may be overwritten by the next call only after this one's reads
+        return c_local
+
+    def close(self):
+        close = getattr(self.engine, "close", None)
+        if close:
+            close()
+
+
+class _null:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False
