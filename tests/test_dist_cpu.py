@@ -1,0 +1,92 @@
+"""The multi-GPU orchestration (row blocks, panel broadcast of B) on two CPU ranks over gloo.
+
+The product path has no CPU implementation, so the ranks here get an engine that answers set_a / panel / full with the
+CPU checker; what is under test is the host logic of ozaki_blackwell_b200/dist.py: the partition of rows, the panel
+ranges, that every rank receives every panel of B from the source rank, and that the assembled result is bit-identical
+to the unsharded product.
+"""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, HERE)
+sys.path.insert(0, os.path.dirname(HERE))
+
+
+class CheckerEngine:
+    """set_a / panel / full of the CUDA engine, answered by the CPU checker on torch CPU tensors."""
+
+    def __init__(self, nm):
+        self.nm, self.A, self.calls = nm, None, []
+
+    def set_a(self, a, stream):
+        self.A = a.numpy().copy()
+
+    def panel(self, b_panel, c, j0, ncols, stream):
+        import oracle_lib as o
+        self.calls.append((j0, ncols))
+        c[:, j0:j0 + ncols] = torch.from_numpy(o.dgemm(self.A, b_panel.numpy(), self.nm))
+
+    def full(self, a, b, c, stream):
+        import oracle_lib as o
+        c.copy_(torch.from_numpy(o.dgemm(a.numpy(), b.numpy(), self.nm)))
+
+
+def _worker(rank, world, port, M, N, K, nm, panels, src, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from ozaki_blackwell_b200.dist import RowShardedGemm, row_block
+    rng = np.random.default_rng(123)
+    A = rng.uniform(-1, 1, (M, K)) * 2.0 ** rng.integers(-8, 9, (M, K))
+    B = rng.uniform(-1, 1, (K, N)) * 2.0 ** rng.integers(-8, 9, (K, N))
+    lo, hi = row_block(M, rank, world)
+    a_local = torch.from_numpy(A[lo:hi].copy())
+    b = torch.from_numpy(B.copy()) if rank == src else None     # only the source rank holds B
+    c_local = torch.zeros((hi - lo, N), dtype=torch.float64)
+    eng = CheckerEngine(nm)
+    op = RowShardedGemm(hi - lo, N, K, nm, src=src, panels=panels, engine=eng, device="cpu")
+    op(a_local, b, c_local)
+    op(a_local, b, c_local)                                     # a second call reuses the staging buffers
+    np.save(os.path.join(out_dir, f"c{rank}.npy"), c_local.numpy())
+    np.save(os.path.join(out_dir, f"calls{rank}.npy"), np.array(eng.calls))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("src", [0, 1])
+def test_two_ranks_match_the_unsharded_product(tmp_path, src):
+    import oracle_lib as o
+    from ozaki_blackwell_b200.dist import panel_ranges, row_block
+    M, N, K, nm, panels, world = 37, 600, 96, 16, 3, 2
+    port = 29500 + (os.getpid() % 2000) + src
+    mp.spawn(_worker, args=(world, port, M, N, K, nm, panels, src, str(tmp_path)), nprocs=world, join=True)
+    rng = np.random.default_rng(123)
+    A = rng.uniform(-1, 1, (M, K)) * 2.0 ** rng.integers(-8, 9, (M, K))
+    B = rng.uniform(-1, 1, (K, N)) * 2.0 ** rng.integers(-8, 9, (K, N))
+    want = o.dgemm(A, B, nm)
+    got = np.vstack([np.load(tmp_path / f"c{r}.npy") for r in range(world)])
+    assert np.array_equal(got.view(np.uint64), want.view(np.uint64))
+    for r in range(world):
+        calls = [tuple(c) for c in np.load(tmp_path / f"calls{r}.npy")]
+        assert calls == [(lo, hi - lo) for lo, hi in panel_ranges(N, panels)] * 2
+    assert row_block(M, 0, world) == (0, 19) and row_block(M, 1, world) == (19, 37)
+
+
+def test_partition_helpers():
+    from ozaki_blackwell_b200.dist import panel_ranges, row_block
+    for m, w in ((8192, 8), (10, 4), (3, 8), (32768, 8)):
+        blocks = [row_block(m, r, w) for r in range(w)]
+        assert blocks[0][0] == 0 and blocks[-1][1] == m
+        assert all(a[1] == b[0] for a, b in zip(blocks, blocks[1:]))
+        assert max(h - l for l, h in blocks) - min(h - l for l, h in blocks) <= 1
+    for n, p in ((8192, 8), (8192, 1), (300, 4), (1000, 3), (256, 8), (32768, 16), (257, 2)):
+        r = panel_ranges(n, p)
+        assert r[0][0] == 0 and r[-1][1] == n and len(r) <= max(p, 1)
+        assert all(a[1] == b[0] for a, b in zip(r, r[1:]))
+        assert all(lo % 256 == 0 for lo, _ in r) and all(hi > lo for lo, hi in r)
