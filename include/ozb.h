@@ -115,6 +115,16 @@ int ozb_scale_residues_rows(int moduli, const double *X, int rows, int len, long
  * as R[l][col][row]); colmax is scratch of `cols` 64-bit words */
 int ozb_scale_residues_cols(int moduli, const double *X, int rows, int cols, long long ldx, int bits, void *colmax, int *s,
                             int8_t *R, int ld, size_t plane, void *stream);
+/* No counterpart in the reference. The column pass of ozb_scale_residues_cols for callers that cannot allocate device
+ * memory when they call: programs whose GPU memory is wholly owned by another allocator (a serving engine or framework
+ * pool that reserved the HBM at start-up), and latency-critical loops that cannot take the device-wide synchronisation
+ * of cudaMalloc / cudaFree. Same arguments minus the scratch: the per-column scratch lives in a fixed array inside the
+ * library (512 KiB on every GPU that loads it, for the life of the process), so `cols` may not exceed 65536
+ * (OZB_ESIZE otherwise). The call allocates nothing. The first call on each device looks up the array's device address
+ * and should therefore be made before any stream capture; all calls on a device share the array (each clears what it
+ * uses, on its stream), so calls that may overlap on the GPU must be ordered by the caller. */
+int ozb_scale_residues_cols_static(int moduli, const double *X, int rows, int cols, long long ldx, int bits, int *s,
+                                   int8_t *R, int ld, size_t plane, void *stream);
 /* src/gemm_i8.cuh:148-160 (oz::gemm_i8_run) -- C[z] = A[z] Bt[z]^T, Z planes, int32 out [Z][M][ldc]. No padding
  * requirement on M, N, K; lda/ldb in bytes, multiples of 16, base pointers 16-byte aligned. */
 int ozb_gemm_i8(const int8_t *A, const int8_t *Bt, int32_t *C, int M, int N, int K, int Z, long long lda, long long ldb,

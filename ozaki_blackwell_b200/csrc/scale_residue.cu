@@ -11,6 +11,7 @@
 // along rows) and a second, transposing pass. The residue of a 64-bit integer is taken from its eight bytes:
 // v + 2^62 = sum b_i 256^i with b_i unsigned, so v mod m = sum b_i (256^i mod m) - (2^62 mod m): two dp4a per modulus
 // and one multiply-high reduction of a 19-bit sum, instead of a 64-bit division by a constant.
+#include <mutex>
 #include "oz_common.cuh"
 
 namespace ozk {
@@ -237,4 +238,60 @@ cudaError_t scale_residues_cols(int nm, const double *X, int rows, int cols, lon
     OZ_DISPATCH_NM(nm, (launch_cols_t<NM>(X, rows, cols, ldx, bits, colmax, s, R, ld, plane, st)));
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Allocation-free variant of the column pass (C ABI: ozb_scale_residues_cols_static)
+// ---------------------------------------------------------------------------------------------------------------
+// For callers that must not allocate device memory at the point of the call: processes that have handed all of the
+// GPU's memory to an allocator of their own (a serving engine or a framework's caching pool that reserved the HBM up
+// front, where a cudaMalloc from a library would fail or fragment the pool), and latency-critical loops that cannot
+// afford cudaMalloc / cudaFree because both synchronise the whole device. The column pass needs one 64-bit word of
+// scratch per column (the running column maxima). Here that scratch is a fixed array in the library's own device image:
+// every GPU that loads the library holds these OZB_STATIC_MAX_COLS * 8 bytes (512 KiB) until the process exits.
+//
+// The array's name is only a host-side handle. Its device address is fetched with cudaGetSymbolAddress, once per device,
+// with that device current, on the first call made on that device -- so the first call on each device should come
+// before any stream capture begins. All calls on one device share the array: it keeps the previous call's maxima, so
+// every call clears the part it uses first (on the caller's stream), and two calls that overlap on the GPU (different
+// streams, no ordering between them) would race on it.
+constexpr int OZB_STATIC_MAX_COLS = 65536;
+static __device__ __align__(256) unsigned long long g_colmax_scratch[OZB_STATIC_MAX_COLS];
+
+static unsigned long long *static_scratch_for_current_device(cudaError_t *err) {
+    static unsigned long long *ptrs[64] = {};
+    static std::mutex mu;
+    int dev = -1;
+    if ((*err = cudaGetDevice(&dev)) != cudaSuccess) return nullptr;
+    if (dev < 0 || dev >= 64) { *err = cudaErrorInvalidDevice; return nullptr; }
+    std::lock_guard<std::mutex> g(mu);
+    if (!ptrs[dev]) {
+        void *p = nullptr;
+        if ((*err = cudaGetSymbolAddress(&p, g_colmax_scratch)) != cudaSuccess) return nullptr;
+        ptrs[dev] = static_cast<unsigned long long *>(p);
+    }
+    *err = cudaSuccess;
+    return ptrs[dev];
+}
+
 }  // namespace ozk
+
+// Same contract as ozb_scale_residues_cols (scales per column of a row-major rows x cols matrix, residues written
+// transposed), without the caller-provided scratch and without any allocation: no cudaMalloc, cudaFree or allocating
+// library routine is called. cols above OZB_STATIC_MAX_COLS (65536) is rejected with OZB_ESIZE (10006).
+extern "C" __attribute__((visibility("default"))) int ozb_scale_residues_cols_static(int moduli, const double *X, int rows, int cols,
+                                                                                    long long ldx, int bits, int *s, int8_t *R, int ld,
+                                                                                    size_t plane, void *stream) {
+    if (rows <= 0 || cols <= 0) return 10001;                       // OZB_EARG
+    if (rows >= 131072) return 10002;                               // OZB_EK
+    if (cols > ozk::OZB_STATIC_MAX_COLS) return 10006;              // OZB_ESIZE: beyond the fixed scratch
+    if (moduli < 8 || moduli > 16 || !X || !s || !R || ldx < cols || ld < (rows + 15) / 16 * 16 || (ld & 15) || (plane & 15) ||
+        (reinterpret_cast<uintptr_t>(R) & 15))
+        return 10001;
+    int dev = 0, major = 0;
+    if (cudaGetDevice(&dev) || cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev)) return (int)cudaGetLastError();
+    if (major != 10) return 10003;                                  // OZB_EARCH
+    cudaError_t e;
+    unsigned long long *scratch = ozk::static_scratch_for_current_device(&e);
+    if (!scratch) return (int)e;
+    // scale_residues_cols clears colmax[0, cols) on the stream before the maxima pass, then runs the two kernels
+    return (int)ozk::scale_residues_cols(moduli, X, rows, cols, ldx, bits, scratch, s, R, ld, plane, (cudaStream_t)stream);
+}
