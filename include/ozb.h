@@ -92,14 +92,17 @@ int ozb_plan_view(ozb_plan *p, int *bits, int *Kp, int *Np, int8_t **Ar, int8_t 
 /* Device status word of the plan: 0, or OZB_ETIMEOUT if a bounded wait expired in a kernel launched through it.
  * Synchronises the stream the last call used. */
 int ozb_plan_status(ozb_plan *p);
-/* Phase timing (src/ozaki2.cuh:135-153, the reference's OZ_PROF): with `slots` > 0 every ozb_plan_dgemm records four
+/* Phase timing (src/ozaki2.cuh:135-153, the reference's OZ_PROF): with `slots` > 0 every ozb_plan_dgemm records
  * events on its stream (no host synchronisation) into slot (call number mod slots); slots = 0 turns it off. A plan
  * created while the environment variable OZ_PROF is set starts with one slot and prints the reference's line on stderr
  * after every product (which synchronises). */
 int ozb_plan_profile(ozb_plan *p, int slots);
-/* Milliseconds of the product recorded in `slot`: ms[0] scales + residues, ms[1] INT8 GEMMs, ms[2] CRT. Waits for that
- * product to finish. */
-int ozb_plan_phase_ms(ozb_plan *p, int slot, float ms[3]);
+/* Milliseconds of the product recorded in `slot`. A product is processed in column panels whose B-residue, GEMM and CRT
+ * stages overlap on internal streams (environment variable OZ_PANELS = 1 keeps one panel and one stream), so the split
+ * is: ms[0] start of the product to the start of the first GEMM (exposed scaling + residues), ms[1] sum of the GEMM
+ * kernels' own durations, ms[2] end of the last GEMM to the end of the product (exposed CRT), ms[3] the whole product.
+ * Waits for that product to finish. */
+int ozb_plan_phase_ms(ozb_plan *p, int slot, float ms[4]);
 
 /* ozb_dgemm with leading dimensions, on device pointers, on a stream, without the final synchronisation. Uses the same
  * cached plan as ozb_dgemm. */

@@ -42,7 +42,7 @@ lib.ozb_plan_panel.argtypes = [_p, _p, _ll, _p, _ll, _i, _i, _p]
 lib.ozb_plan_view.argtypes = [_p, _ip, _ip, _ip] + [ctypes.POINTER(_p)] * 5
 lib.ozb_plan_status.argtypes = [_p]
 lib.ozb_plan_profile.argtypes = [_p, _i]
-lib.ozb_plan_phase_ms.argtypes = [_p, _i, ctypes.POINTER(ctypes.c_float * 3)]
+lib.ozb_plan_phase_ms.argtypes = [_p, _i, ctypes.POINTER(ctypes.c_float * 4)]
 lib.ozb_dgemm_ex.argtypes = [_i, _i, _i, _p, _ll, _p, _ll, _p, _ll, _i, _p]
 lib.ozb_scale_residues_rows.argtypes = [_i, _p, _i, _i, _ll, _i, _p, _p, _i, _sz, _p]
 lib.ozb_scale_residues_cols.argtypes = [_i, _p, _i, _i, _ll, _i, _p, _p, _p, _i, _sz, _p]

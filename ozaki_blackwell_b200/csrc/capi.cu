@@ -32,9 +32,15 @@ struct ozb_plan {
     unsigned long long *colmax;
     cudaStream_t last;
     bool env_prof;                   // OZ_PROF set: one line per product on stderr, as the reference does
-    int slots, calls;                // event ring: 4 events per slot, slot = call number mod slots
+    int slots, calls;                // event ring: EV_PER_SLOT events per slot, slot = call number mod slots
     cudaEvent_t *ev;
+    // column panels of one product: B's residues (stream s1), the GEMMs (caller's stream) and the CRT (stream s2) of
+    // different panels run side by side; panels = 1 keeps everything on the caller's stream
+    int panels, panel_width;
+    cudaStream_t s1, s2;
+    cudaEvent_t evFork, evJoin, evB[8], evG[8];
 };
+constexpr int MAXP = 8, EV_PER_SLOT = 2 + 2 * MAXP;   // start, end, and (start, end) of each panel's GEMM
 
 static int round_up(int x, int to) { return (x + to - 1) / to * to; }
 
@@ -49,28 +55,39 @@ static int bits_for_impl(int nm, int K, int maxbits) {   // src/ozaki2.cuh:101-1
 static void plan_free(ozb_plan *p) {
     if (!p) return;
     cudaFree(p->Ar); cudaFree(p->Br); cudaFree(p->Cr); cudaFree(p->sa); cudaFree(p->sb); cudaFree(p->status); cudaFree(p->colmax);
-    for (int i = 0; i < 4 * p->slots; i++) cudaEventDestroy(p->ev[i]);
+    for (int i = 0; i < EV_PER_SLOT * p->slots; i++) cudaEventDestroy(p->ev[i]);
     delete[] p->ev;
+    if (p->s1) cudaStreamDestroy(p->s1);
+    if (p->s2) cudaStreamDestroy(p->s2);
+    if (p->evFork) cudaEventDestroy(p->evFork);
+    if (p->evJoin) cudaEventDestroy(p->evJoin);
+    for (int i = 0; i < MAXP; i++) { if (p->evB[i]) cudaEventDestroy(p->evB[i]); if (p->evG[i]) cudaEventDestroy(p->evG[i]); }
     delete p;
 }
 
 static int plan_profile(ozb_plan *p, int slots) {
-    for (int i = 0; i < 4 * p->slots; i++) cudaEventDestroy(p->ev[i]);
+    for (int i = 0; i < EV_PER_SLOT * p->slots; i++) cudaEventDestroy(p->ev[i]);
     delete[] p->ev;
     p->ev = nullptr; p->slots = 0; p->calls = 0;
     if (slots <= 0) return 0;
-    p->ev = new cudaEvent_t[4 * slots];
-    for (int i = 0; i < 4 * slots; i++)
+    p->ev = new cudaEvent_t[EV_PER_SLOT * slots];
+    for (int i = 0; i < EV_PER_SLOT * slots; i++)
         if (cudaError_t e = cudaEventCreate(&p->ev[i])) { for (int j = 0; j < i; j++) cudaEventDestroy(p->ev[j]); delete[] p->ev; p->ev = nullptr; return (int)e; }
     p->slots = slots;
     return 0;
 }
-static int plan_phase_ms(ozb_plan *p, int slot, float ms[3]) {
+// ms[0]: start of the product to the start of the first GEMM (exposed scaling + residues); ms[1]: sum of the GEMM
+// kernels' durations; ms[2]: end of the last GEMM to the end of the product (exposed CRT); ms[3]: the whole product
+static int plan_phase_ms(ozb_plan *p, int slot, float ms[4]) {
     if (slot < 0 || slot >= p->slots || slot >= p->calls) return OZB_EARG;
-    cudaEvent_t *ev = p->ev + 4 * slot;
-    if (cudaError_t e = cudaEventSynchronize(ev[3])) return (int)e;
-    for (int i = 0; i < 3; i++) if (cudaError_t e = cudaEventElapsedTime(&ms[i], ev[i], ev[i + 1])) return (int)e;
-    return 0;
+    cudaEvent_t *ev = p->ev + EV_PER_SLOT * slot;
+    if (cudaError_t e = cudaEventSynchronize(ev[1])) return (int)e;
+    cudaError_t e = cudaEventElapsedTime(&ms[0], ev[0], ev[2]);
+    ms[1] = 0;
+    for (int q = 0; q < p->panels && !e; q++) { float t; e = cudaEventElapsedTime(&t, ev[2 + 2 * q], ev[3 + 2 * q]); ms[1] += t; }
+    if (!e) e = cudaEventElapsedTime(&ms[2], ev[3 + 2 * (p->panels - 1)], ev[1]);
+    if (!e) e = cudaEventElapsedTime(&ms[3], ev[0], ev[1]);
+    return (int)e;
 }
 
 static int plan_make(int M, int N, int K, int nm, int maxbits, ozb_plan **out) {
@@ -89,6 +106,21 @@ static int plan_make(int M, int N, int K, int nm, int maxbits, ozb_plan **out) {
     if (!e) e = cudaMalloc(&p->colmax, (size_t)N * 8);
     if (!e) e = cudaMalloc(&p->status, 4);
     if (!e) e = cudaMemset(p->status, 0, 4);
+    // panels: OZ_PANELS overrides; default one panel per 2048 columns (at least N/8), none below 4096 columns
+    p->panel_width = round_up(N, 256); p->panels = 1;
+    {
+        const char *env = getenv("OZ_PANELS");
+        int want = env && *env ? atoi(env) : (N >= 4096 ? (N + 2047) / 2048 : 1);
+        if (want > MAXP) want = MAXP;
+        if (want > 1) { p->panel_width = round_up((N + want - 1) / want, 256); p->panels = (N + p->panel_width - 1) / p->panel_width; }
+    }
+    if (!e && p->panels > 1) {
+        e = cudaStreamCreateWithFlags(&p->s1, cudaStreamNonBlocking);
+        if (!e) e = cudaStreamCreateWithFlags(&p->s2, cudaStreamNonBlocking);
+        if (!e) e = cudaEventCreateWithFlags(&p->evFork, cudaEventDisableTiming);
+        if (!e) e = cudaEventCreateWithFlags(&p->evJoin, cudaEventDisableTiming);
+        for (int i = 0; i < MAXP && !e; i++) { e = cudaEventCreateWithFlags(&p->evB[i], cudaEventDisableTiming); if (!e) e = cudaEventCreateWithFlags(&p->evG[i], cudaEventDisableTiming); }
+    }
     p->env_prof = getenv("OZ_PROF") != nullptr;
     if (!e && p->env_prof) e = (cudaError_t)plan_profile(p, 1);
     if (e) { cudaGetLastError(); plan_free(p); return (int)e; }
@@ -118,20 +150,43 @@ static int plan_panel(ozb_plan *p, const double *B, long long ldb, double *C, lo
 }
 static int plan_dgemm(ozb_plan *p, const double *A, long long lda, const double *B, long long ldb, double *C, long long ldc,
                       cudaStream_t st) {
-    cudaEvent_t *ev = p->slots ? p->ev + 4 * (p->calls % p->slots) : nullptr;
+    cudaEvent_t *ev = p->slots ? p->ev + EV_PER_SLOT * (p->calls % p->slots) : nullptr;
+    const bool multi = p->panels > 1;
+    cudaStream_t s1 = multi ? p->s1 : st, s2 = multi ? p->s2 : st;
+    p->last = st;
     if (ev) cudaEventRecord(ev[0], st);
-    if (int e = plan_set_a(p, A, lda, st)) return e;
-    if (int e = plan_panel(p, B, ldb, C, ldc, 0, p->N, st, ev)) return e;
+    if (multi) { cudaEventRecord(p->evFork, st); cudaStreamWaitEvent(s1, p->evFork, 0); }
+    cudaError_t e = scale_residues_rows(p->nm, A, p->M, p->K, lda, p->bits, p->sa, p->Ar, p->Kp, p->planeA, st);
+    for (int q = 0; q < p->panels && !e; q++) {   // B: maxima + residues of every panel, queued on s1 ahead of the GEMMs
+        const int j0 = q * p->panel_width, n = (p->N - j0 < p->panel_width) ? p->N - j0 : p->panel_width;
+        e = scale_residues_cols(p->nm, B + j0, p->K, n, ldb, p->bits, p->colmax + j0, p->sb + j0, p->Br + (size_t)j0 * p->Kp, p->Kp,
+                                p->planeB, s1);
+        if (multi && !e) e = cudaEventRecord(p->evB[q], s1);
+    }
+    for (int q = 0; q < p->panels && !e; q++) {
+        const int j0 = q * p->panel_width, n = (p->N - j0 < p->panel_width) ? p->N - j0 : p->panel_width;
+        if (multi) cudaStreamWaitEvent(st, p->evB[q], 0);
+        if (ev) cudaEventRecord(ev[2 + 2 * q], st);
+        e = gemm_i8_planes(p->Ar, p->Br + (size_t)j0 * p->Kp, p->Cr + j0, p->M, n, p->K, p->nm, p->Kp, p->Kp, p->Np, p->planeA, p->planeB,
+                           p->planeC, 1, 0, p->status, 0, st);
+        if (ev) cudaEventRecord(ev[3 + 2 * q], st);
+        if (e) break;
+        if (multi) { cudaEventRecord(p->evG[q], st); cudaStreamWaitEvent(s2, p->evG[q], 0); }
+        e = crt_from_i8(p->nm, p->Cr + j0, p->planeC, p->M, n, p->Np, p->sa, p->sb + j0, C + j0, ldc, s2);
+    }
+    if (multi) { cudaEventRecord(p->evJoin, s2); cudaStreamWaitEvent(st, p->evJoin, 0); }
+    if (e) return (int)e;
     if (ev) {
-        cudaEventRecord(ev[3], st);
+        cudaEventRecord(ev[1], st);
         const int slot = p->calls % p->slots;
         p->calls++;
         if (p->calls >= 0x40000000) p->calls = p->slots;   // keep the counter bounded; every slot stays readable
         if (p->env_prof) {   // src/ozaki2.cuh:147-152: one line per product on stderr (this synchronises, like the reference)
-            float ms[3];
+            float ms[4];
             if (!plan_phase_ms(p, slot, ms))
-                fprintf(stderr, "oz%d %dx%dx%d: scale+residues %.3f  INT8 GEMMs %.3f (%.0f TOPS)  CRT %.3f ms\n", p->nm, p->M, p->N,
-                        p->K, ms[0], ms[1], 2.0 * p->nm * p->M * (double)p->N * p->K / (ms[1] * 1e9), ms[2]);
+                fprintf(stderr, "oz%d %dx%dx%d: scale+residues %.3f  INT8 GEMMs %.3f (%.0f TOPS)  CRT %.3f ms  (total %.3f, %d panels)\n",
+                        p->nm, p->M, p->N, p->K, ms[0], ms[1], 2.0 * p->nm * p->M * (double)p->N * p->K / (ms[1] * 1e9), ms[2], ms[3],
+                        p->panels);
         }
     }
     return 0;
@@ -340,7 +395,7 @@ OZB_API int ozb_plan_profile(ozb_plan *p, int slots) {
     std::lock_guard<std::mutex> g(mu);
     return plan_profile(p, slots);
 }
-OZB_API int ozb_plan_phase_ms(ozb_plan *p, int slot, float ms[3]) {
+OZB_API int ozb_plan_phase_ms(ozb_plan *p, int slot, float ms[4]) {
     if (!p || !ms) return OZB_EARG;
     std::lock_guard<std::mutex> g(mu);
     return plan_phase_ms(p, slot, ms);

@@ -156,40 +156,55 @@ __global__ void __launch_bounds__(256) col_absmax(const double *__restrict__ X, 
 
 // ---------------------------------------------------------------------------------------------------------------
 // B side, pass 2: residues of a row-major K x N matrix written transposed, Rt[l][j][k].
-// Block 256 threads = 8 warps; lane = column, each warp owns 32 consecutive k (two runs of 16), so that reads are
-// 256-byte row segments and every thread writes whole 16-byte pieces of its column's K-contiguous output row.
+// Block: 256 threads, tile of 32 columns x 128 k. Phase 1: lane = column, warp w owns k in [16w, 16w + 16): reads are
+// 256-byte row segments, each thread produces 16 bytes per plane and parks them in shared memory, S[l][j][k] with rows
+// padded to 144 bytes (conflict-free for 16-byte accesses both ways). Phase 2: the tile is written out row by row,
+// eight threads per 128-byte row, so every store instruction writes four full 128-byte lines.
 // ---------------------------------------------------------------------------------------------------------------
+constexpr int CT_COLS = 32, CT_K = 128, CT_PITCH = CT_K + 16;
+template <int NM> constexpr int col_tile_smem() { return NM * CT_COLS * CT_PITCH; }
+
 template <int NM>
 __global__ void __launch_bounds__(256) col_residues_t(const double *__restrict__ X, int rows, int cols, long long ldx,
                                                       const unsigned long long *__restrict__ colmax, int bits,
                                                       int *__restrict__ s_out, int8_t *__restrict__ Rp, int ld, size_t plane) {
+    extern __shared__ __align__(16) uint8_t tile[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int j = blockIdx.x * 32 + lane;
-    const int kbase = blockIdx.y * 256 + warp * 32;
-    if (j >= cols || kbase >= rows) return;
-    const int s = scale_from_max(__longlong_as_double((long long)colmax[j]), bits);
-    if (blockIdx.y == 0 && warp == 0) s_out[j] = s;
-    const bool fast = s >= -1022 && s <= 1023;
-    const double p2 = pow2_normal(fast ? s : 0);
-    int8_t *out = Rp + (size_t)j * ld;
-#pragma unroll 1
-    for (int half = 0; half < 2; half++) {
-        const int k0 = kbase + half * 16;
-        if (k0 >= rows) break;
-        double d[16];
+    const int j0 = blockIdx.x * CT_COLS, kb = blockIdx.y * CT_K;
+    {
+        const int j = j0 + lane, k0 = kb + warp * 16;
+        if (j < cols && k0 < rows) {
+            const int s = scale_from_max(__longlong_as_double((long long)colmax[j]), bits);
+            if (blockIdx.y == 0 && warp == 0) s_out[j] = s;
+            const bool fast = s >= -1022 && s <= 1023;
+            const double p2 = pow2_normal(fast ? s : 0);
+            double d[16];
 #pragma unroll
-        for (int e = 0; e < 16; e++) d[e] = k0 + e < rows ? X[(size_t)(k0 + e) * ldx + j] : 0.0;
-        uint32_t w[NM][4];
+            for (int e = 0; e < 16; e++) d[e] = k0 + e < rows ? X[(size_t)(k0 + e) * ldx + j] : 0.0;
+            uint32_t w[NM][4];
 #pragma unroll
-        for (int q = 0; q < 4; q++) {
-            long long v[4];
+            for (int q = 0; q < 4; q++) {
+                long long v[4];
 #pragma unroll
-            for (int e = 0; e < 4; e++) v[e] = scaled_int(d[4 * q + e], s, p2, fast);
-            residues_of_4<NM>(v, [&](auto L, uint32_t word) { w[decltype(L)::value][q] = word; });
+                for (int e = 0; e < 4; e++) v[e] = scaled_int(d[4 * q + e], s, p2, fast);
+                residues_of_4<NM>(v, [&](auto L, uint32_t word) { w[decltype(L)::value][q] = word; });
+            }
+#pragma unroll
+            for (int l = 0; l < NM; l++)
+                *reinterpret_cast<uint4 *>(tile + (l * CT_COLS + lane) * CT_PITCH + warp * 16) = make_uint4(w[l][0], w[l][1], w[l][2], w[l][3]);
         }
-#pragma unroll
-        for (int l = 0; l < NM; l++)
-            *reinterpret_cast<uint4 *>(out + l * plane + k0) = make_uint4(w[l][0], w[l][1], w[l][2], w[l][3]);
+    }
+    __syncthreads();
+    const int c = threadIdx.x & 7;                 // 16-byte piece of the 128-byte row
+    const int kpos = kb + c * 16;
+    if (kpos >= rows) return;                      // pieces wholly beyond K are never read by the GEMM (TMA extent = K)
+#pragma unroll 4
+    for (int i = 0; i < NM; i++) {                 // rows of the tile: (l, j), 32 per pass
+        const int j = threadIdx.x >> 3, l = i;
+        if (j0 + j < cols) {
+            const uint4 v = *reinterpret_cast<const uint4 *>(tile + (l * CT_COLS + j) * CT_PITCH + c * 16);
+            *reinterpret_cast<uint4 *>(Rp + (size_t)l * plane + (size_t)(j0 + j) * ld + kpos) = v;
+        }
     }
 }
 
@@ -213,7 +228,10 @@ static cudaError_t launch_cols_t(const double *X, int rows, int cols, long long 
     cudaError_t e = cudaMemsetAsync(colmax, 0, (size_t)cols * 8, st);
     if (e) return e;
     col_absmax<<<dim3((cols + 511) / 512, (rows + CM_ROWS - 1) / CM_ROWS), 256, 0, st>>>(X, rows, cols, ldx, colmax);
-    col_residues_t<NM><<<dim3((cols + 31) / 32, (rows + 255) / 256), 256, 0, st>>>(X, rows, cols, ldx, colmax, bits, s, R, ld, plane);
+    static const cudaError_t attr = cudaFuncSetAttribute(col_residues_t<NM>, cudaFuncAttributeMaxDynamicSharedMemorySize, col_tile_smem<NM>());
+    if (attr) return attr;
+    col_residues_t<NM><<<dim3((cols + CT_COLS - 1) / CT_COLS, (rows + CT_K - 1) / CT_K), 256, col_tile_smem<NM>(), st>>>(
+        X, rows, cols, ldx, colmax, bits, s, R, ld, plane);
     return cudaGetLastError();
 }
 
