@@ -104,13 +104,13 @@ static int plan_make(int M, int N, int K, int nm, int maxbits, ozb_plan **out) {
     if (!e) e = cudaMalloc(&p->sa, (size_t)M * 4);
     if (!e) e = cudaMalloc(&p->sb, (size_t)N * 4);
     if (!e) e = cudaMalloc(&p->colmax, (size_t)N * 8);
-    if (!e) e = cudaMalloc(&p->status, 4);
-    if (!e) e = cudaMemset(p->status, 0, 4);
-    // panels: OZ_PANELS overrides; default one panel per 2048 columns (at least N/8), none below 4096 columns
+    if (!e) e = cudaMalloc(&p->status, 256);
+    if (!e) e = cudaMemset(p->status, 0, 256);
+    // panels: one by default; OZ_PANELS = 2..8 splits the columns and overlaps the stages of different panels
     p->panel_width = round_up(N, 256); p->panels = 1;
     {
         const char *env = getenv("OZ_PANELS");
-        int want = env && *env ? atoi(env) : (N >= 4096 ? (N + 2047) / 2048 : 1);
+        int want = env && *env ? atoi(env) : 1;   // measured on B200: overlapping the stages slows the GEMMs by more than it hides
         if (want > MAXP) want = MAXP;
         if (want > 1) { p->panel_width = round_up((N + want - 1) / want, 256); p->panels = (N + p->panel_width - 1) / p->panel_width; }
     }
@@ -191,13 +191,26 @@ static int plan_dgemm(ozb_plan *p, const double *A, long long lda, const double 
     }
     return 0;
 }
+// status words: [0] the first wait code of a launch that gave up (0 = none), [1..63] per-CTA codes for diagnostics
+static int read_status(int *dev_words) {
+    int h[64] = {};
+    if (cudaError_t e = cudaMemcpy(h, dev_words, sizeof h, cudaMemcpyDeviceToHost)) return (int)e;
+    if (getenv("OZ_DEBUG") && (h[8] | h[9] | h[10] | h[11]))   // timing build of the pair kernel: (wait, total) in 1024-cycle units
+        fprintf(stderr, "ozb: cta0 producer %d/%d issuer %d/%d | cta1 producer %d/%d issuer %d/%d\n", h[8], h[9], h[10], h[11], h[12], h[13],
+                h[14], h[15]);
+    if (!h[0]) return 0;
+    cudaMemset(dev_words, 0, sizeof h);
+    if (getenv("OZ_DEBUG")) {
+        fprintf(stderr, "ozb: a wait expired, first code 0x%x; per CTA:", h[0]);
+        for (int i = 1; i < 64; i++) if (h[i]) fprintf(stderr, " [%d]=0x%x", i - 1, h[i]);
+        fprintf(stderr, "\n");
+    }
+    return OZB_ETIMEOUT;
+}
 static int plan_status(ozb_plan *p) {
-    int h = 0;
     cudaError_t e = cudaStreamSynchronize(p->last);
-    if (!e) e = cudaMemcpy(&h, p->status, 4, cudaMemcpyDeviceToHost);
     if (e) return (int)e;
-    if (h) { cudaMemset(p->status, 0, 4); return OZB_ETIMEOUT; }
-    return 0;
+    return read_status(p->status);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -228,7 +241,7 @@ int *status_word() {
     int dev = 0;
     if (cudaGetDevice(&dev) || dev < 0 || dev >= 64) return nullptr;
     if (!stage_status[dev]) {
-        if (cudaMalloc(&stage_status[dev], 4) || cudaMemset(stage_status[dev], 0, 4)) { cudaGetLastError(); stage_status[dev] = nullptr; }
+        if (cudaMalloc(&stage_status[dev], 256) || cudaMemset(stage_status[dev], 0, 256)) { cudaGetLastError(); stage_status[dev] = nullptr; }
     }
     return stage_status[dev];
 }
@@ -462,8 +475,5 @@ OZB_API int ozb_status(void) {
     if (int e = (int)cudaDeviceSynchronize()) return e;
     int *st = status_word();
     if (!st) return (int)cudaErrorMemoryAllocation;
-    int h = 0;
-    if (int e = (int)cudaMemcpy(&h, st, 4, cudaMemcpyDeviceToHost)) return e;
-    if (h) { cudaMemset(st, 0, 4); return OZB_ETIMEOUT; }
-    return 0;
+    return read_status(st);
 }

@@ -18,6 +18,8 @@
 // band and the B panels in flight stay in L2. Every mbarrier wait is bounded: on expiry the CTA raises a status word,
 // stops issuing, releases its tensor memory and returns.
 #include <cuda.h>
+#include <cstdio>
+#include <cstdlib>
 #include "oz_common.cuh"
 
 namespace ozk {
@@ -62,7 +64,7 @@ __device__ __forceinline__ unsigned long long now_ns() {
 }
 // Bounded wait: each wait has its own budget, started the first time the spin loop looks at the clock. Returns false
 // when the budget ran out or another role of this CTA already gave up (*abort_flag != 0).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int who = 1) {
     unsigned long long deadline = 0;
     for (uint32_t spin = 0;; spin++) {
         if (mbar_try(bar, parity)) return true;
@@ -70,7 +72,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             if (*abort_flag) return false;
             const unsigned long long t = now_ns();
             if (!deadline) deadline = t + WAIT_NS;
-            else if (t > deadline) { *abort_flag = 1; return false; }
+            else if (t > deadline) { *abort_flag = who; return false; }   // who: which wait gave up (diagnostics)
         }
     }
 }
@@ -273,7 +275,248 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_i8_tc(const __grid_constant__
         __syncwarp();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
     }
-    if (threadIdx.x == 0 && abort_flag) atomicExch(p.status, 1);
+    if (threadIdx.x == 0 && abort_flag) {   // word 0: the first code of the launch; words 1..63: per-CTA codes (diagnostics)
+        atomicCAS(p.status, 0, abort_flag);
+        if (blockIdx.x < 63) p.status[1 + blockIdx.x] = abort_flag;
+    }
+}
+
+
+// ---------------------------------------------------------------------------------------------------------------
+// Two-CTA variant (cta_group::2): a cluster of two CTAs on one TPC works on one 256 x 256 tile.
+// Each CTA loads its own 128 rows of A and its own 128 of the 256 rows of Bt (half the shared-memory fill and read
+// traffic per tensor operation of the one-CTA kernel, so 6 stages of 32 KB fit instead of 4 of 48 KB); the leader CTA
+// (cluster rank 0) issues tcgen05.mma.cta_group::2 with M = 256, and every CTA finds its 128 rows of the accumulator in
+// its own tensor memory. Signals cross the pair like this:
+//   full[s]      lives in the leader: its producer expects the bytes of both CTAs, and both producers point their TMA
+//                loads at it (cp.async.bulk.tensor with .cta_group::2 may complete on the peer's barrier; no multicast);
+//   empty[s]     one per CTA. The issuer commits to the leader's; the leader's producer, once it has seen its own
+//                stage free, passes that on to the peer's barrier with a plain remote mbarrier.arrive;
+//   accfull[a]   one per CTA, same relay (by the leader's first epilogue warp);
+//   accempty[a]  lives in the leader; the 8 epilogue warps of the pair arrive on it.
+// Only mbarrier.arrive crosses the pair; tcgen05.commit always targets the issuing CTA's own barriers.
+// ---------------------------------------------------------------------------------------------------------------
+namespace two {
+constexpr int BM2 = 256;                            // rows of A per pair (128 per CTA)
+constexpr int STAGES2 = 6;
+constexpr int HALF_B = (BN / 2) * BKB;              // this CTA's 128 rows of Bt per stage
+constexpr int STAGE2_BYTES = A_BYTES + HALF_B;      // 16 KB + 16 KB
+constexpr int SMEM2_BYTES = STAGES2 * STAGE2_BYTES + 1024 + 256;
+constexpr uint32_t IDESC2 = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM2 >> 4) << 24);
+}  // namespace two
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {   // the same shared-memory offset in CTA `rank`
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
+    // default semantics (release at CTA scope): a cluster-scope release here stalled the arriving thread for ~1400 cycles
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap *map, int c0, int c1, int c2, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void mma_i8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(two::IDESC2), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void mma_commit_pair(uint32_t bar) {   // bar: a barrier of the issuing (leader) CTA
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// the epilogue of one 32-column piece of one accumulator row: shared by both kernels
+template <bool FUSED_MOD>
+__device__ __forceinline__ void store_piece(const Params &p, const ModConsts &mc, const uint32_t (&v)[32], int z, int row, int col) {
+    if (row >= p.M || col >= p.N) return;
+    if constexpr (FUSED_MOD) {
+        uint32_t o[8];
+#pragma unroll
+        for (int g = 0; g < 8; g++) {
+            uint32_t x[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const uint32_t u = v[4 * g + e] ^ 0x80000000u;                 // product + 2^31, non-negative
+                const uint32_t t = (u >> 16) * mc.c16 + (u & 0xFFFFu) + mc.adj;  // same class mod m, below 2^24 + 2^16
+                x[e] = t - __umulhi(t, mc.magic) * mc.m - (uint32_t)mc.half;     // balanced residue
+            }
+            o[g] = pack_low_bytes(x[0], x[1], x[2], x[3]);
+        }
+        int8_t *dst = reinterpret_cast<int8_t *>(p.C) + (size_t)z * p.plane_c + (size_t)row * p.ldc + col;
+        if (col + 16 <= p.ldc) *reinterpret_cast<uint4 *>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
+        if (col + 32 <= p.ldc) *reinterpret_cast<uint4 *>(dst + 16) = make_uint4(o[4], o[5], o[6], o[7]);
+    } else {
+        int32_t *dst = reinterpret_cast<int32_t *>(p.C) + (size_t)z * p.plane_c + (size_t)row * p.ldc + col;
+        if (col + 32 <= p.N && ((p.ldc | p.plane_c) & 3) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0) {
+#pragma unroll
+            for (int g = 0; g < 8; g++)
+                reinterpret_cast<uint4 *>(dst)[g] = make_uint4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 32; e++)
+                if (col + e < p.N) dst[e] = (int32_t)v[e];
+        }
+    }
+}
+
+template <bool FUSED_MOD>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+gemm_i8_tc2(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const Params p) {
+    using namespace two;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bars = base + STAGES2 * STAGE2_BYTES;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (STAGES2 + s); };
+    auto accfull_bar = [&](int a) { return bars + 8u * (2 * STAGES2 + a); };
+    auto accempty_bar = [&](int a) { return bars + 8u * (2 * STAGES2 + 2 + a); };
+    const uint32_t tmem_slot = bars + 8u * (2 * STAGES2 + 4);
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();          // 0 = leader
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < STAGES2; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int a = 0; a < 2; a++) { mbar_init(accfull_bar(a), 1); mbar_init(accempty_bar(a), 8); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {   // warp 1 of both CTAs allocates together
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"((uint32_t)TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();                             // the peer's barriers exist before anything arrives on them
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    uint32_t tmem_base;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
+
+    const int tiles_m2 = (p.M + BM2 - 1) / BM2;
+    Params pp = p;                                  // decode_work over 256-row tiles
+    pp.tiles_m = tiles_m2;
+    const int total = tiles_m2 * p.tiles_n * p.Z;
+    const int kblocks = (p.K + BKB - 1) / BKB;
+    const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+    volatile int *abortp = &abort_flag;
+#ifdef OZ_TIMING
+    long long t_wait = 0, t_all = clock64();
+#define OZ_T0 const long long t0_ = clock64();
+#define OZ_T1 t_wait += clock64() - t0_;
+#else
+#define OZ_T0
+#define OZ_T1
+#endif
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (int w = pair; w < total && !*abortp; w += npairs) {
+                int z, tm, tn;
+                decode_work(pp, w, z, tm, tn);
+                for (int kb = 0; kb < kblocks; kb++, it++) {
+                    const int s = it % STAGES2;
+                    OZ_T0
+                    if (!mbar_wait(empty_bar(s), ((it / STAGES2) & 1u) ^ 1u, abortp, 0x10 + (int)rank + ((int)(it & 0xfff) << 8))) break;
+                    OZ_T1
+                    const uint32_t lead_full = map_to_cta(full_bar(s), 0);
+                    if (rank == 0) {
+                        if (it >= STAGES2) mbar_arrive_cluster(map_to_cta(empty_bar(s), 1));   // the stage is free in the peer too
+                        mbar_expect_tx(full_bar(s), 2 * STAGE2_BYTES);                          // both CTAs' bytes land here
+                    }
+                    const uint32_t sa = base + s * STAGE2_BYTES;
+                    tma_load_3d_pair(sa, &mapA, kb * BKB, tm * BM2 + (int)rank * BM, z, lead_full);
+                    tma_load_3d_pair(sa + A_BYTES, &mapB, kb * BKB, tn * BN + (int)rank * (BN / 2), z, lead_full);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            uint32_t it = 0, n = 0;
+            for (int w = pair; w < total && !*abortp; w += npairs, n++) {
+                const uint32_t acc = n & 1u;
+                if (!mbar_wait(accempty_bar(acc), ((n >> 1) & 1u) ^ 1u, abortp, 0x20 + ((int)(n & 0xfff) << 8))) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
+                bool ok = true;
+                for (int kb = 0; kb < kblocks; kb++, it++) {
+                    const int s = it % STAGES2;
+                    OZ_T0
+                    if (!mbar_wait(full_bar(s), (it / STAGES2) & 1u, abortp, 0x30 + ((int)(it & 0xfff) << 8))) { ok = false; break; }
+                    OZ_T1
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t sa = base + s * STAGE2_BYTES;
+                    const uint64_t da = smem_desc(sa), db = smem_desc(sa + A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BKB / UK; k++) mma_i8_pair(d_tmem, da + 2u * k, db + 2u * k, (kb | k) != 0);
+                    mma_commit_pair(empty_bar(s));
+                }
+                if (!ok) break;
+                mma_commit_pair(accfull_bar(acc));
+            }
+        }
+    } else {
+        const int q = warp & 3;
+        ModConsts mc{};
+        uint32_t n = 0;
+        for (int w = pair; w < total && !*abortp; w += npairs, n++) {
+            int z, tm, tn;
+            decode_work(pp, w, z, tm, tn);
+            const uint32_t acc = n & 1u;
+            if constexpr (FUSED_MOD) mc = c_modc[p.first_modulus + z];
+            if (!__all_sync(~0u, mbar_wait(accfull_bar(acc), (n >> 1) & 1u, abortp, 0x40 + (int)rank + ((int)(n & 0xfff) << 8)))) break;
+            if (rank == 0 && warp == 2 && lane == 0) mbar_arrive_cluster(map_to_cta(accfull_bar(acc), 1));   // tell the peer's epilogue
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int row = tm * BM2 + (int)rank * BM + q * 32 + lane;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * ACC_COLS;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; c++) {
+                uint32_t v[32];
+                tmem_ld32(taddr + c * 32, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                store_piece<FUSED_MOD>(p, mc, v, z, row, tn * BN + c * 32);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(accempty_bar(acc), 0));
+        }
+    }
+
+#ifdef OZ_TIMING
+    if (blockIdx.x < 2 && lane == 0 && warp < 2) {   // words 8..: [cta][warp] = (wait cycles, total cycles) in units of 1024 cycles
+        p.status[8 + (blockIdx.x * 2 + warp) * 2] = (int)(t_wait >> 10);
+        p.status[9 + (blockIdx.x * 2 + warp) * 2] = (int)((clock64() - t_all) >> 10);
+    }
+#endif
+    // teardown: nobody may leave while the peer can still signal into this CTA's shared memory
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (warp == 1) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
+    }
+    if (threadIdx.x == 0 && abort_flag) {   // word 0: the first code of the launch; words 1..63: per-CTA codes (diagnostics)
+        atomicCAS(p.status, 0, abort_flag);
+        if (blockIdx.x < 63) p.status[1 + blockIdx.x] = abort_flag;
+    }
 }
 
 }  // namespace g8
@@ -319,7 +562,11 @@ static cudaError_t gemm_setup() {
         if (e) return e;
         e = cudaFuncSetAttribute(g8::gemm_i8_tc<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, g8::SMEM_BYTES);
         if (e) return e;
-        return cudaFuncSetAttribute(g8::gemm_i8_tc<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, g8::SMEM_BYTES);
+        e = cudaFuncSetAttribute(g8::gemm_i8_tc<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, g8::SMEM_BYTES);
+        if (e) return e;
+        e = cudaFuncSetAttribute(g8::gemm_i8_tc2<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, g8::two::SMEM2_BYTES);
+        if (e) return e;
+        return cudaFuncSetAttribute(g8::gemm_i8_tc2<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, g8::two::SMEM2_BYTES);
     }();
     return once;
 }
@@ -335,9 +582,13 @@ cudaError_t gemm_i8_planes(const int8_t *A, const int8_t *Bt, void *C, int M, in
     if (fused && ((ldc & 15) || first_modulus < 0 || first_modulus + Z > MAXM)) return cudaErrorInvalidValue;
     cudaError_t e = gemm_setup();
     if (e) return e;
+    // OZ_GEMM_CTAS=1 selects the one-CTA kernel; the default pairs CTAs (cta_group::2) once there are two tile rows
+    static const int want_pair = [] { const char *env = getenv("OZ_GEMM_CTAS"); return !(env && *env == '1'); }();
+    const bool pair = want_pair && M > g8::BM;
     CUtensorMap mapA, mapB;
     if ((e = make_map(&mapA, A, K, M, Z, lda, pa, g8::BM))) return e;
-    if ((e = make_map(&mapB, Bt, K, N, Z, ldb, pb, g8::BN))) return e;
+    // the TMA box must match the stage layout: a whole 256-row B tile per CTA, or this CTA's 128-row half in a pair
+    if ((e = make_map(&mapB, Bt, K, N, Z, ldb, pb, pair ? g8::BN / 2 : g8::BN))) return e;
     g8::Params p{};
     p.M = M; p.N = N; p.K = K; p.Z = Z;
     p.tiles_m = (M + g8::BM - 1) / g8::BM;
@@ -352,6 +603,30 @@ cudaError_t gemm_i8_planes(const int8_t *A, const int8_t *Bt, void *C, int M, in
     }
     const long long total = (long long)p.tiles_m * p.tiles_n * Z;
     if (total > 0x7fffffffLL) return cudaErrorInvalidValue;
+    if (pair) {
+        // A persistent grid must be fully resident: ask how many 2-CTA clusters of this kernel the device can hold at once
+        static int max_pairs[2] = {0, 0};
+        if (!max_pairs[fused ? 1 : 0]) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(sms & ~1); cfg.blockDim = dim3(g8::THREADS); cfg.dynamicSmemBytes = g8::two::SMEM2_BYTES;
+            cudaLaunchAttribute at[1];
+            at[0].id = cudaLaunchAttributeClusterDimension; at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+            cfg.attrs = at; cfg.numAttrs = 1;
+            int n = 0;
+            cudaError_t q = fused ? cudaOccupancyMaxActiveClusters(&n, g8::gemm_i8_tc2<true>, &cfg)
+                                  : cudaOccupancyMaxActiveClusters(&n, g8::gemm_i8_tc2<false>, &cfg);
+            if (q != cudaSuccess || n <= 0) { cudaGetLastError(); n = sms / 2; }
+            if (n > sms / 2) n = sms / 2;
+            max_pairs[fused ? 1 : 0] = n;
+            if (getenv("OZ_DEBUG")) fprintf(stderr, "ozb: %d SMs, at most %d resident CTA pairs\n", sms, n);
+        }
+        const long long pairs_total = (long long)((M + g8::two::BM2 - 1) / g8::two::BM2) * p.tiles_n * Z;
+        const int limit = max_pairs[fused ? 1 : 0];
+        const int pairs = (int)(pairs_total < limit ? pairs_total : limit);
+        if (fused) g8::gemm_i8_tc2<true><<<2 * pairs, g8::THREADS, g8::two::SMEM2_BYTES, st>>>(mapA, mapB, p);
+        else g8::gemm_i8_tc2<false><<<2 * pairs, g8::THREADS, g8::two::SMEM2_BYTES, st>>>(mapA, mapB, p);
+        return cudaGetLastError();
+    }
     const int grid = (int)(total < sms ? total : sms);
     if (fused) g8::gemm_i8_tc<true><<<grid, g8::THREADS, g8::SMEM_BYTES, st>>>(mapA, mapB, p);
     else g8::gemm_i8_tc<false><<<grid, g8::THREADS, g8::SMEM_BYTES, st>>>(mapA, mapB, p);
