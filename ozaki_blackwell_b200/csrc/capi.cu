@@ -23,6 +23,7 @@ using namespace ozk;
 // ---------------------------------------------------------------------------------------------------------------
 // plan
 // ---------------------------------------------------------------------------------------------------------------
+constexpr int HOST_PANELS = 8;
 struct ozb_plan {
     int M, N, K, nm, bits, maxbits;
     int Kp, Np;                      // pitch of the residue planes of A and B (bytes); pitch of the product planes (bytes)
@@ -39,6 +40,10 @@ struct ozb_plan {
     int panels, panel_width;
     cudaStream_t s1, s2;
     cudaEvent_t evFork, evJoin, evB[8], evG[8];
+    // host operands (on_host = 1): device copies kept with the plan, three streams, one event pair per column panel
+    double *hA, *hB, *hC;
+    cudaStream_t sIn, sRun, sOut;
+    cudaEvent_t evIn[HOST_PANELS + 1], evRun[HOST_PANELS];
 };
 constexpr int MAXP = 8, EV_PER_SLOT = 2 + 2 * MAXP;   // start, end, and (start, end) of each panel's GEMM
 
@@ -62,6 +67,12 @@ static void plan_free(ozb_plan *p) {
     if (p->evFork) cudaEventDestroy(p->evFork);
     if (p->evJoin) cudaEventDestroy(p->evJoin);
     for (int i = 0; i < MAXP; i++) { if (p->evB[i]) cudaEventDestroy(p->evB[i]); if (p->evG[i]) cudaEventDestroy(p->evG[i]); }
+    cudaFree(p->hA); cudaFree(p->hB); cudaFree(p->hC);
+    if (p->sIn) cudaStreamDestroy(p->sIn);
+    if (p->sRun) cudaStreamDestroy(p->sRun);
+    if (p->sOut) cudaStreamDestroy(p->sOut);
+    for (auto &e : p->evIn) if (e) cudaEventDestroy(e);
+    for (auto &e : p->evRun) if (e) cudaEventDestroy(e);
     delete p;
 }
 
@@ -191,6 +202,52 @@ static int plan_dgemm(ozb_plan *p, const double *A, long long lda, const double 
     }
     return 0;
 }
+// Host operands (python/capi.cu:37-48,82-88 stage everything, compute, copy back). Here the three phases overlap: A goes
+// first, then B in column panels; each panel is scaled, multiplied and reconstructed as soon as it has landed, and its
+// columns of C travel back while the next panel is being computed. With pinned host memory the copies are asynchronous
+// and the product hides behind the transfer of B; with pageable memory the calls below block in issue order and the
+// result is the same. The device copies stay with the plan (freed by ozb_release).
+static int plan_dgemm_host(ozb_plan *p, const double *A, const double *B, double *C) {
+    const size_t M = p->M, N = p->N, K = p->K;
+    cudaError_t e = cudaSuccess;
+    if (!p->hA) {
+        e = cudaMalloc(&p->hA, M * K * 8);
+        if (!e) e = cudaMalloc(&p->hB, K * N * 8);
+        if (!e) e = cudaMalloc(&p->hC, M * N * 8);
+        if (!e) e = cudaStreamCreateWithFlags(&p->sIn, cudaStreamNonBlocking);
+        if (!e) e = cudaStreamCreateWithFlags(&p->sRun, cudaStreamNonBlocking);
+        if (!e) e = cudaStreamCreateWithFlags(&p->sOut, cudaStreamNonBlocking);
+        for (auto &ev : p->evIn) if (!e) e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+        for (auto &ev : p->evRun) if (!e) e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+        if (e) return (int)e;
+    }
+    int panels = (p->N + 1023) / 1024;           // about 1024 columns each, starts on multiples of 256
+    if (panels > HOST_PANELS) panels = HOST_PANELS;
+    if (panels < 1) panels = 1;
+    const int width = round_up((p->N + panels - 1) / panels, 256);
+    panels = (p->N + width - 1) / width;
+    e = cudaMemcpyAsync(p->hA, A, M * K * 8, cudaMemcpyHostToDevice, p->sIn);
+    if (!e) e = cudaEventRecord(p->evIn[0], p->sIn);
+    if (!e) e = cudaStreamWaitEvent(p->sRun, p->evIn[0], 0);
+    if (!e) e = (cudaError_t)plan_set_a(p, p->hA, (long long)K, p->sRun);
+    for (int q = 0; q < panels && !e; q++) {
+        const int j0 = q * width, n = (p->N - j0 < width) ? p->N - j0 : width;
+        e = cudaMemcpy2DAsync(p->hB + j0, N * 8, B + j0, N * 8, (size_t)n * 8, K, cudaMemcpyHostToDevice, p->sIn);
+        if (!e) e = cudaEventRecord(p->evIn[q + 1], p->sIn);
+        if (!e) e = cudaStreamWaitEvent(p->sRun, p->evIn[q + 1], 0);
+        if (!e) e = (cudaError_t)plan_panel(p, p->hB + j0, (long long)N, p->hC + j0, (long long)N, j0, n, p->sRun, nullptr);
+        if (!e) e = cudaEventRecord(p->evRun[q], p->sRun);
+        if (!e) e = cudaStreamWaitEvent(p->sOut, p->evRun[q], 0);
+        if (!e) e = cudaMemcpy2DAsync(C + j0, N * 8, p->hC + j0, N * 8, (size_t)n * 8, M, cudaMemcpyDeviceToHost, p->sOut);
+    }
+    if (!e) e = cudaStreamSynchronize(p->sOut);
+    cudaError_t e2 = cudaStreamSynchronize(p->sRun), e3 = cudaStreamSynchronize(p->sIn);
+    p->last = p->sRun;
+    if (e) return (int)e;
+    if (e2) return (int)e2;
+    return (int)e3;
+}
+
 // status words: [0] the first wait code of a launch that gave up (0 = none), [1..63] per-CTA codes for diagnostics
 static int read_status(int *dev_words) {
     int h[64] = {};
@@ -284,20 +341,9 @@ OZB_API int ozb_dgemm(int M, int N, int K, const double *A, const double *B, dou
         if (int e = finish()) return e;
         return plan_status(p);
     }
-    // host operands: stage through device buffers (python/capi.cu:37-48,82-88)
-    double *dA = nullptr, *dB = nullptr, *dC = nullptr;
-    const size_t la = (size_t)M * K * 8, lb = (size_t)K * N * 8, lc = (size_t)M * N * 8;
-    int e = (int)cudaMalloc(&dA, la);
-    if (!e) e = (int)cudaMalloc(&dB, lb);
-    if (!e) e = (int)cudaMalloc(&dC, lc);
-    if (!e) e = (int)cudaMemcpy(dA, A, la, cudaMemcpyHostToDevice);
-    if (!e) e = (int)cudaMemcpy(dB, B, lb, cudaMemcpyHostToDevice);
-    if (!e) e = plan_dgemm(p, dA, K, dB, N, dC, N, 0);
-    if (!e) e = finish();
-    if (!e) e = plan_status(p);
-    if (!e) e = (int)cudaMemcpy(C, dC, lc, cudaMemcpyDeviceToHost);
-    cudaFree(dA); cudaFree(dB); cudaFree(dC);
-    return e;
+    if (int e = plan_dgemm_host(p, A, B, C)) return e;
+    if (int e = finish()) return e;
+    return plan_status(p);
 }
 
 OZB_API int ozb_ddgemm(int M, int N, int K, const double *, const double *, const double *, const double *, double *, double *, int) {

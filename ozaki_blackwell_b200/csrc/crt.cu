@@ -56,6 +56,13 @@ __device__ __forceinline__ double garner_horner(uint32_t (&X)[(NM + 3) / 4]) {
     return y;
 }
 
+// ldexp(y, e) as the reference applies it (src/ozaki2.cuh:96). For e in the normal exponent range 2^e is a double and the
+// product y * 2^e is a single correctly rounded operation, which is what ldexp returns (exact unless the result is
+// subnormal, rounded once if it is, infinite on overflow); other exponents take ldexp itself.
+__device__ __forceinline__ double unscale(double y, int e) {
+    return (e >= -1022 && e <= 1023) ? y * pow2_normal(e) : ldexp(y, e);
+}
+
 // balanced residue of a raw int32 product (reference layout of the planes)
 template <int L>
 __device__ __forceinline__ int balanced_of_i32(int32_t x) {
@@ -109,7 +116,7 @@ __global__ void __launch_bounds__(256) crt_kernel(const In *__restrict__ Cp, siz
 #pragma unroll
     for (int e = 0; e < 4; e++) {
         const double y = garner_horner<NM>(E[e]);
-        out[e] = j0 + e < N ? ldexp(y, -(si + sb[j0 + e])) : 0.0;
+        out[e] = j0 + e < N ? unscale(y, -(si + sb[j0 + e])) : 0.0;
     }
     double *dst = C + (size_t)i * ldc + j0;
     if (j0 + 3 < N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
