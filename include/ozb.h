@@ -142,6 +142,11 @@ int ozb_crt_i32(int moduli, const int32_t *Cl, size_t plane, int M, int N, long 
 /* the same from int8 planes of balanced residues (ldr a multiple of 4) */
 int ozb_crt_i8(int moduli, const int8_t *Cr, size_t plane, int M, int N, long long ldr, const int *sa, const int *sb,
                double *C, long long ldc, void *stream);
+/* bench/peak.cu:20-58 (the reference's register-only mma.sync peak) -- the INT8 rate of this GPU's tensor cores with
+ * nothing else running: every SM issues the GEMM kernel's tcgen05.mma shape back to back on one shared-memory stage of
+ * pseudo-random bytes, `iters` (1..2^22) rounds of 8 instructions per CTA (pair = 0) or per CTA pair (pair = 1,
+ * cta_group::2). Synchronous. Returns the elapsed ms and tera-operations per second (2 ops per multiply-add). */
+int ozb_int8_peak(int iters, int pair, float *ms, double *tops);
 /* Status of the stage calls above (they share one device status word per device): 0 or OZB_ETIMEOUT. Synchronises
  * the device. */
 int ozb_status(void);

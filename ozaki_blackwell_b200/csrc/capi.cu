@@ -517,6 +517,13 @@ OZB_API int ozb_crt_i8(int moduli, const int8_t *Cr, size_t plane, int M, int N,
         return OZB_EARG;
     return (int)crt_from_i8(moduli, Cr, plane, M, N, ldr, sa, sb, C, ldc, (cudaStream_t)stream);
 }
+OZB_API int ozb_int8_peak(int iters, int pair, float *ms, double *tops) {
+    if (int e = check_args(1, 1, 1)) return e;
+    int *st = status_word();
+    if (!st) return (int)cudaErrorMemoryAllocation;
+    if (int e = (int)int8_peak_probe(iters, pair, ms, tops, st, 0)) return e == (int)cudaErrorInvalidValue ? OZB_EARG : e;
+    return read_status(st);
+}
 OZB_API int ozb_status(void) {
     if (int e = (int)cudaDeviceSynchronize()) return e;
     int *st = status_word();

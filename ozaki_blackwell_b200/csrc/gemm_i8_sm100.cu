@@ -519,6 +519,75 @@ gemm_i8_tc2(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
     }
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------
+// Tensor-pipe probe: the INT8 rate this GPU sustains when nothing but tcgen05.mma runs (the counterpart of the
+// reference's register-only mma.sync peak, bench/peak.cu:20-58). Every CTA (or CTA pair) fills one shared-memory stage
+// with pseudo-random bytes once and then issues the GEMM kernel's own instruction shape back to back on it, alternating
+// between the two accumulators; there is no TMA and no epilogue inside the timed loop. The result is the roofline the
+// GEMM kernel is measured against: it includes whatever the power limit does to the clock under full tensor load.
+// ---------------------------------------------------------------------------------------------------------------
+template <bool PAIR>
+__global__ void __launch_bounds__(THREADS, 1) tensor_peak_probe(int iters, int *status) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bar = base + STAGE_BYTES, tmem_slot = bar + 16;
+    __shared__ int abort_flag;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint32_t rank = 0;
+    if constexpr (PAIR) rank = cluster_rank();
+    if (threadIdx.x == 0) { abort_flag = 0; mbar_init(bar, 1); asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+    {   // fill the stage: 48 KB of hashed bytes (random data draws the power real residues draw)
+        uint32_t x = 0x9E3779B9u * (blockIdx.x * THREADS + threadIdx.x + 1);
+        uint32_t *w = reinterpret_cast<uint32_t *>(smem_raw + (base - smem_u32(smem_raw)));
+        for (int i = threadIdx.x; i < STAGE_BYTES / 4; i += THREADS) { x ^= x << 13; x ^= x >> 17; x ^= x << 5; w[i] = x; }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the tensor core's reads
+    }
+    if (warp == 1) {
+        if constexpr (PAIR) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"((uint32_t)TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"((uint32_t)TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if constexpr (PAIR) cluster_sync_all();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    uint32_t tmem_base;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
+    if (warp == 1 && lane == 0 && rank == 0) {
+        const uint64_t da = smem_desc(base), db = smem_desc(base + A_BYTES);
+        uint32_t phase = 0;
+        for (int it = 0; it < iters && !abort_flag; it++) {
+#pragma unroll
+            for (int a = 0; a < 2; a++)
+#pragma unroll
+                for (int k = 0; k < BKB / UK; k++) {
+                    if constexpr (PAIR) mma_i8_pair(tmem_base + a * ACC_COLS, da + 2u * k, db + 2u * k, 1u);
+                    else mma_i8(tmem_base + a * ACC_COLS, da + 2u * k, db + 2u * k, 1u);
+                }
+            if ((it & 15) == 15 || it == iters - 1) {   // bound the work in flight: wait for everything issued so far
+                if constexpr (PAIR) mma_commit_pair(bar); else mma_commit(bar);
+                if (!mbar_wait(bar, phase, &abort_flag, 0x50)) break;
+                phase ^= 1u;
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if constexpr (PAIR) cluster_sync_all();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (warp == 1) {
+        __syncwarp();
+        if constexpr (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
+        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
+    }
+    if (threadIdx.x == 0 && abort_flag) atomicCAS(status, 0, abort_flag);
+}
+
 }  // namespace g8
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -631,6 +700,50 @@ cudaError_t gemm_i8_planes(const int8_t *A, const int8_t *Bt, void *C, int M, in
     if (fused) g8::gemm_i8_tc<true><<<grid, g8::THREADS, g8::SMEM_BYTES, st>>>(mapA, mapB, p);
     else g8::gemm_i8_tc<false><<<grid, g8::THREADS, g8::SMEM_BYTES, st>>>(mapA, mapB, p);
     return cudaGetLastError();
+}
+
+
+// Runs the tensor-pipe probe on every SM for `iters` rounds of 8 MMAs per CTA (pair = 1: cta_group::2, 8 M-256 MMAs
+// per pair) and reports the time and the INT8 rate. `status` as for gemm_i8_planes.
+cudaError_t int8_peak_probe(int iters, int pair, float *ms, double *tops, int *status, cudaStream_t st) {
+    if (iters <= 0 || iters > (1 << 22)) return cudaErrorInvalidValue;
+    cudaError_t e = gemm_setup();
+    if (e) return e;
+    static const cudaError_t attr = [] {
+        cudaError_t a = cudaFuncSetAttribute(g8::tensor_peak_probe<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, g8::SMEM_BYTES);
+        return a ? a : cudaFuncSetAttribute(g8::tensor_peak_probe<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, g8::SMEM_BYTES);
+    }();
+    if (attr) return attr;
+    int dev, sms;
+    if ((e = cudaGetDevice(&dev))) return e;
+    if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev))) return e;
+    cudaEvent_t e0, e1;
+    if ((e = cudaEventCreate(&e0))) return e;
+    if ((e = cudaEventCreate(&e1))) { cudaEventDestroy(e0); return e; }
+    const int grid = sms & ~1;
+    cudaEventRecord(e0, st);
+    if (pair) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(grid); cfg.blockDim = dim3(g8::THREADS); cfg.dynamicSmemBytes = g8::SMEM_BYTES; cfg.stream = st;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension; at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+        cfg.attrs = at; cfg.numAttrs = 1;
+        e = cudaLaunchKernelEx(&cfg, g8::tensor_peak_probe<true>, iters, status);
+    } else {
+        g8::tensor_peak_probe<false><<<grid, g8::THREADS, g8::SMEM_BYTES, st>>>(iters, status);
+        e = cudaGetLastError();
+    }
+    cudaEventRecord(e1, st);
+    if (!e) e = cudaEventSynchronize(e1);
+    float t = 0;
+    if (!e) e = cudaEventElapsedTime(&t, e0, e1);
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
+    if (e) return e;
+    const double per_mma = 2.0 * g8::BM * g8::BN * g8::UK * (pair ? 2 : 1);
+    const double units = pair ? grid / 2 : grid;
+    if (ms) *ms = t;
+    if (tops) *tops = units * (double)iters * 8.0 * per_mma / (t * 1e-3) / 1e12;
+    return cudaSuccess;
 }
 
 }  // namespace ozk
