@@ -343,7 +343,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--n", type=int, default=8192)
+    ap.add_argument("--size", "--n", dest="n", type=int, default=8192, help="n of the n x n x n product (use --size under torchrun)")
     ap.add_argument("--moduli", type=int, default=16)
     ap.add_argument("--panels", type=int, default=4)
     ap.add_argument("--strong", action="store_true", help="strong scaling: the n x n x n product is split over the ranks")

@@ -111,6 +111,7 @@ struct Params {
     int M, N, K, Z;               // rows of A, rows of Bt, inner length, planes
     int tiles_m, tiles_n, band;   // tile grid of one plane and the band height (tile rows)
     int first_modulus;            // plane z reduces mod modulus(first_modulus + z) in the fused mode
+    int accumulate;               // fused mode: add the residues already stored in C (a previous K chunk) before reducing
     void *C;                      // int32 [Z][M][ldc] or int8 [Z][M][ldc]
     long long ldc;                // row pitch of C in elements
     size_t plane_c;               // plane pitch of C in elements
@@ -346,19 +347,25 @@ template <bool FUSED_MOD>
 __device__ __forceinline__ void store_piece(const Params &p, const ModConsts &mc, const uint32_t (&v)[32], int z, int row, int col) {
     if (row >= p.M || col >= p.N) return;
     if constexpr (FUSED_MOD) {
+        int8_t *dst = reinterpret_cast<int8_t *>(p.C) + (size_t)z * p.plane_c + (size_t)row * p.ldc + col;
+        uint32_t prev[8] = {};
+        if (p.accumulate) {   // residues of the K chunks before this one: residues add, |sum| stays far below 2^31
+            if (col + 16 <= p.ldc) { const uint4 q = *reinterpret_cast<const uint4 *>(dst); prev[0] = q.x; prev[1] = q.y; prev[2] = q.z; prev[3] = q.w; }
+            if (col + 32 <= p.ldc) { const uint4 q = *reinterpret_cast<const uint4 *>(dst + 16); prev[4] = q.x; prev[5] = q.y; prev[6] = q.z; prev[7] = q.w; }
+        }
         uint32_t o[8];
 #pragma unroll
         for (int g = 0; g < 8; g++) {
             uint32_t x[4];
 #pragma unroll
             for (int e = 0; e < 4; e++) {
-                const uint32_t u = v[4 * g + e] ^ 0x80000000u;                 // product + 2^31, non-negative
+                const int add = (int)(int8_t)(prev[g] >> (8 * e));
+                const uint32_t u = (v[4 * g + e] + (uint32_t)add) ^ 0x80000000u;   // product (+ earlier chunks) + 2^31, non-negative
                 const uint32_t t = (u >> 16) * mc.c16 + (u & 0xFFFFu) + mc.adj;  // same class mod m, below 2^24 + 2^16
                 x[e] = t - __umulhi(t, mc.magic) * mc.m - (uint32_t)mc.half;     // balanced residue
             }
             o[g] = pack_low_bytes(x[0], x[1], x[2], x[3]);
         }
-        int8_t *dst = reinterpret_cast<int8_t *>(p.C) + (size_t)z * p.plane_c + (size_t)row * p.ldc + col;
         if (col + 16 <= p.ldc) *reinterpret_cast<uint4 *>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
         if (col + 32 <= p.ldc) *reinterpret_cast<uint4 *>(dst + 16) = make_uint4(o[4], o[5], o[6], o[7]);
     } else {
@@ -643,11 +650,12 @@ static cudaError_t gemm_setup() {
 // C[z] = A[z] * Bt[z]^T for z < Z. A: [Z][M][lda] int8, Bt: [Z][N][ldb] int8 (pitches in bytes, multiples of 16; plane
 // pitches pa, pb). fused = 0: C is int32 [Z][M][ldc]. fused = 1: C is int8 [Z][M][ldc] holding the balanced residue of
 // plane z mod modulus(first_modulus + z); ldc must then be a multiple of 16 with the padding columns writable.
-// `status` is a device int the kernel sets to 1 if a barrier wait expired. `sms` = 0 uses every SM.
+// `status` is a device int the kernel sets if a barrier wait expired. `sms` = 0 uses every SM. accumulate = 1 (fused mode only)
+// adds the residues already in C before reducing: the caller splits a long K into chunks whose panels stay in L2.
 cudaError_t gemm_i8_planes(const int8_t *A, const int8_t *Bt, void *C, int M, int N, int K, int Z, long long lda, long long ldb,
                            long long ldc, size_t pa, size_t pb, size_t pc, int fused, int first_modulus, int *status, int sms,
-                           cudaStream_t st) {
-    if (M <= 0 || N <= 0 || K <= 0 || Z <= 0) return cudaErrorInvalidValue;
+                           cudaStream_t st, int accumulate) {
+    if (M <= 0 || N <= 0 || K <= 0 || Z <= 0 || (accumulate && !fused)) return cudaErrorInvalidValue;
     if (fused && ((ldc & 15) || first_modulus < 0 || first_modulus + Z > MAXM)) return cudaErrorInvalidValue;
     cudaError_t e = gemm_setup();
     if (e) return e;
@@ -664,6 +672,7 @@ cudaError_t gemm_i8_planes(const int8_t *A, const int8_t *Bt, void *C, int M, in
     p.tiles_n = (N + g8::BN - 1) / g8::BN;
     p.band = 8;
     p.first_modulus = first_modulus;
+    p.accumulate = accumulate;
     p.C = C; p.ldc = ldc; p.plane_c = pc; p.status = status;
     if (sms <= 0) {
         int dev;

@@ -40,6 +40,17 @@ def test_odd_shapes_bit_exact(shape):
     assert g.same_bits(got, want), g.describe_mismatch(got, want)
 
 
+@pytest.mark.parametrize("shape", [(70, 300, 12289), (40, 520, 20000), (260, 64, 33000)])
+def test_long_k_is_cut_into_chunks_bit_exact(shape):
+    """K above 12288 runs as several GEMM launches whose residues accumulate: same bits as the one-pass definition."""
+    g = _gu()
+    M, N, K = shape
+    A, B = g.synthetic(M, K, 18), g.synthetic(K, N, 19)
+    got = g.gpu_dgemm(A, B, 16)
+    want = o.dgemm(A, B, 16)
+    assert g.same_bits(got, want), g.describe_mismatch(got, want)
+
+
 def test_host_operands_match_device_operands():
     g = _gu()
     A, B = g.synthetic(130, 700, 7), g.synthetic(700, 90, 8)
