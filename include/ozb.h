@@ -109,6 +109,12 @@ int ozb_plan_phase_ms(ozb_plan *p, int slot, float ms[4]);
 int ozb_dgemm_ex(int M, int N, int K, const double *A, long long lda, const double *B, long long ldb, double *C,
                  long long ldc, int moduli, void *stream);
 
+/* src/ozaki_dd.cuh:143-148 (oz::ddgemm_t) -- the double-double product with leading dimensions (elements), the
+ * reference's mode (0: C = AB, 1: C -= AB, 2: C = -AB, used by its LU solvers to update blocks in place), a modulus
+ * count in {24, 28, 32} and a stream; device pointers, no final synchronisation. */
+int ozb_ddgemm_ex(int M, int N, int K, const double *Ah, const double *Al, long long lda, const double *Bh, const double *Bl,
+                  long long ldb, double *Ch, double *Cl, long long ldo, int moduli, int mode, void *stream);
+
 /* The four stages on caller-owned device buffers (what bench/phases.cu launches one by one). Asynchronous.
  * Pitches: ld of int8 planes in bytes and a multiple of 16; `plane` = distance between planes in elements. */
 /* src/ozaki2.cuh:56-78 -- scales + residues of an A-like operand (rows of `len` contiguous doubles, pitch ldx) */

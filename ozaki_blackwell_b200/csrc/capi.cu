@@ -216,6 +216,18 @@ static int plan_dgemm(ozb_plan *p, const double *A, long long lda, const double 
     }
     return 0;
 }
+// src/ozaki_dd.cuh:145-155 (ddgemm_t): scales from the hi parts, residues of hi + lo, the same INT8 GEMMs, direct-sum CRT.
+// lda, ldb, ldo in elements; mode 0: C = AB, 1: C -= AB, 2: C = -AB.
+static int plan_ddgemm(ozb_plan *p, const double *Ah, const double *Al, long long lda, const double *Bh, const double *Bl, long long ldb,
+                       double *Ch, double *Cl, long long ldo, int mode, cudaStream_t st) {
+    p->last = st;
+    cudaError_t e = dd_scale_residues_rows(p->nm, Ah, Al, p->M, p->K, lda, p->bits, p->sa, p->Ar, p->Kp, p->planeA, st);
+    if (!e) e = dd_scale_residues_cols(p->nm, Bh, Bl, p->K, p->N, ldb, p->bits, p->colmax, p->sb, p->Br, p->Kp, p->planeB, st);
+    if (!e) e = gemm_chunks(p, p->Br, p->Cr, p->N, st);
+    if (!e) e = dd_crt_from_i8(p->nm, p->Cr, p->planeC, p->M, p->N, p->Np, p->sa, p->sb, Ch, Cl, ldo, mode, st);
+    return (int)e;
+}
+
 // Host operands (python/capi.cu:37-48,82-88 stage everything, compute, copy back). Here the three phases overlap: A goes
 // first, then B in column panels; each panel is scaled, multiplied and reconstructed as soon as it has landed, and its
 // columns of C travel back while the next panel is being computed. With pinned host memory the copies are asynchronous
@@ -360,9 +372,45 @@ OZB_API int ozb_dgemm(int M, int N, int K, const double *A, const double *B, dou
     return plan_status(p);
 }
 
-OZB_API int ozb_ddgemm(int M, int N, int K, const double *, const double *, const double *, const double *, double *, double *, int) {
+OZB_API int ozb_ddgemm(int M, int N, int K, const double *Ah, const double *Al, const double *Bh, const double *Bl, double *Ch,
+                       double *Cl, int on_host) {   // python/capi.cu:92-105
     if (int e = check_args(M, N, K)) return e;
-    return OZB_ENOTBUILT;
+    std::lock_guard<std::mutex> g(mu);
+    ozb_plan *p;
+    if (int e = plan_for(1, M, N, K, 32, 106, &p)) return e;
+    if (!on_host) {
+        if (int e = plan_ddgemm(p, Ah, Al, K, Bh, Bl, N, Ch, Cl, N, 0, 0)) return e;
+        if (int e = finish()) return e;
+        return plan_status(p);
+    }
+    // host operands: staged through device buffers (python/capi.cu:37-48,98-104)
+    const double *in[4] = {Ah, Al, Bh, Bl};
+    const size_t len[4] = {(size_t)M * K, (size_t)M * K, (size_t)K * N, (size_t)K * N}, lo = (size_t)M * N;
+    double *d[6] = {};
+    int e = 0;
+    for (int i = 0; i < 6 && !e; i++) e = (int)cudaMalloc(&d[i], (i < 4 ? len[i] : lo) * 8);
+    for (int i = 0; i < 4 && !e; i++) e = (int)cudaMemcpy(d[i], in[i], len[i] * 8, cudaMemcpyHostToDevice);
+    if (!e) e = plan_ddgemm(p, d[0], d[1], K, d[2], d[3], N, d[4], d[5], N, 0, 0);
+    if (!e) e = finish();
+    if (!e) e = plan_status(p);
+    if (!e) e = (int)cudaMemcpy(Ch, d[4], lo * 8, cudaMemcpyDeviceToHost);
+    if (!e) e = (int)cudaMemcpy(Cl, d[5], lo * 8, cudaMemcpyDeviceToHost);
+    for (double *x : d) if (x) cudaFree(x);
+    return e;
+}
+
+// src/ozaki_dd.cuh:143-148 -- the double-double product with leading dimensions, a mode and a stream, on device pointers,
+// without the final synchronisation. moduli in {24, 28, 32}; mode 0: C = AB, 1: C -= AB, 2: C = -AB.
+OZB_API int ozb_ddgemm_ex(int M, int N, int K, const double *Ah, const double *Al, long long lda, const double *Bh, const double *Bl,
+                          long long ldb, double *Ch, double *Cl, long long ldo, int moduli, int mode, void *stream) {
+    if (int e = check_args(M, N, K)) return e;
+    if ((moduli != 24 && moduli != 28 && moduli != 32) || mode < 0 || mode > 2 || !Ah || !Al || !Bh || !Bl || !Ch || !Cl || lda < K ||
+        ldb < N || ldo < N)
+        return OZB_EARG;
+    std::lock_guard<std::mutex> g(mu);
+    ozb_plan *p;
+    if (int e = plan_for(1, M, N, K, moduli, 106, &p)) return e;
+    return plan_ddgemm(p, Ah, Al, lda, Bh, Bl, ldb, Ch, Cl, ldo, mode, (cudaStream_t)stream);
 }
 
 OZB_API int ozb_tdgemm(int M, int N, int K, const double *, const double *, const double *, const double *, const double *,
@@ -376,10 +424,46 @@ OZB_API void ozb_release(void) {
     for (Cache &c : cache) if (c.p) { plan_free(c.p); c.p = nullptr; }
 }
 
+static int bench_dd(int n, int reps, double *median_ms) {   // python/capi.cu:130-164, kind 1: lower parts 2^-53 below
+    const size_t len = (size_t)n * n;
+    double *d[6] = {};   // Ah, Al, Ch, Cl, Bh, Bl
+    int err = 0;
+    for (int i = 0; i < 6 && !err; i++) err = (int)cudaMalloc(&d[i], len * sizeof(double));
+    if (!err) {
+        double *h = (double *)malloc(len * sizeof(double));
+        if (!h) err = (int)cudaErrorMemoryAllocation;
+        for (int i = 0; i < 4 && !err; i++) {
+            const double sc = i % 2 == 0 ? 1.0 : 0x1p-53;
+            uint64_t x = 0x9E3779B97F4A7C15ull * (i + 1);
+            for (size_t j = 0; j < len; j++) { x ^= x << 13; x ^= x >> 7; x ^= x << 17; h[j] = sc * ((double)(x >> 11) * 0x1p-52 - 1.0); }
+            err = (int)cudaMemcpy(d[i < 2 ? i : 2 + i], h, len * sizeof(double), cudaMemcpyHostToDevice);
+        }
+        free(h);
+    }
+    float t[101]; int nt = 0;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    if (!err) { cudaEventCreate(&e0); cudaEventCreate(&e1); }
+    for (int r = -1; r < reps && !err; r++) {
+        cudaEventRecord(e0);
+        err = ozb_ddgemm(n, n, n, d[0], d[1], d[4], d[5], d[2], d[3], 0);
+        cudaEventRecord(e1); cudaEventSynchronize(e1);
+        float ms; cudaEventElapsedTime(&ms, e0, e1);
+        if (r >= 0) t[nt++] = ms;
+    }
+    if (nt) {
+        for (int i = 1; i < nt; i++) for (int j = i; j > 0 && t[j - 1] > t[j]; j--) { const float x = t[j]; t[j] = t[j - 1]; t[j - 1] = x; }
+        *median_ms = t[nt / 2];
+    }
+    if (e0) { cudaEventDestroy(e0); cudaEventDestroy(e1); }
+    for (double *p : d) if (p) cudaFree(p);
+    return err;
+}
+
 OZB_API int ozb_bench(int n, int kind, int reps, double *median_ms) {   // python/capi.cu:130-164
     if (int e = check_args(n, n, n)) return e;
     if (kind < 0 || kind > 2 || reps < 1 || reps > 101 || !median_ms) return OZB_EARG;
-    if (kind != 0) return OZB_ENOTBUILT;
+    if (kind == 2) return OZB_ENOTBUILT;
+    if (kind == 1) return bench_dd(n, reps, median_ms);
     const size_t len = (size_t)n * n;
     double *d[3] = {};
     int err = 0;

@@ -7,7 +7,8 @@
 //
 // How: the reference spends l modular reductions on digit l (120 at 16 moduli). Here the recurrence is unrolled into one
 // signed dot product per digit (see garner_p / garner_q in oz_tables.cuh), evaluated with dp4a on digits packed four to
-// a register, and reduced once: 39 dp4a and 15 multiply-high reductions per element. The digits are the same integers
+// a register, and reduced once: 39 dp4a and 15 multiply-high reductions per element; a thread runs its four elements in
+// lockstep so that they share the coefficient words. The digits are the same integers
 // (a balanced digit is unique in its residue class), so the FP64 Horner loop sees the same operands in the same order.
 // Input is either the GEMM epilogue's int8 planes of already balanced residues (16 bytes per element at 16 moduli
 // instead of 64) or, for the reference's layout, int32 planes of raw products.
@@ -25,34 +26,53 @@ __device__ __forceinline__ void transpose4x4(const uint32_t (&in)[4], uint32_t (
     out[3] = __byte_perm(b, d, 0x7632);
 }
 
-// One element: X[g] holds the balanced residues r_{4g}..r_{4g+3} as int8 (unused bytes zero). Returns y of the Horner loop.
-template <int NM>
-__device__ __forceinline__ double garner_horner(uint32_t (&X)[(NM + 3) / 4]) {
-    double d[NM];
-    d[0] = (double)(int)(int8_t)(X[0] & 255);   // modulus 256: the residue is the digit
-    static_for<1, NM>([&](auto L) {
-        constexpr int l = decltype(L)::value, m = modulus(l);
+// Garner digits of E elements in lockstep, in place: on entry X[e][g] holds the balanced residues r_{4g}..r_{4g+3} of
+// element e as int8 (unused bytes zero), on exit the balanced mixed-radix digits x_{4g}..x_{4g+3}. Running the elements
+// side by side lets them share every coefficient word and keeps the state to (NM+3)/4 registers per element.
+template <int NM, int E>
+__device__ __forceinline__ void garner_digits(uint32_t (&X)[E][(NM + 3) / 4]) {
+    static_for<1, NM>([&](auto L) {   // digit 0 is the residue mod 256 itself
+        constexpr int l = decltype(L)::value;
         constexpr int lift = lift_of(l, GARNER_BOUND);
         static_assert(magic_ok(l, (uint64_t)lift + GARNER_BOUND), "multiply-high reduction out of range");
-        int acc = lift;
+        int acc[E];
+#pragma unroll
+        for (int e = 0; e < E; e++) acc[e] = lift;
         // digits x_0..x_{l-1} have already replaced the residues in the low bytes; byte l still holds r_l
         static_for<0, l / 4 + 1>([&](auto G) {
             constexpr int g = decltype(G)::value;
             constexpr auto coef = [](int idx) constexpr { return idx < l ? garner_q(idx, l) : (idx == l ? garner_p(l) : 0); };
             constexpr uint32_t cw = pack4(coef(4 * g), coef(4 * g + 1), coef(4 * g + 2), coef(4 * g + 3));
-            acc = dp4a_ss(X[g], cw, acc);
-        });
-        const uint32_t r = mod_magic<l>((uint32_t)acc);            // (x_l + floor(m/2)) in [0, m)
-        const uint32_t xl = r - (uint32_t)half_of(l);
-        constexpr uint32_t sel = l % 4 == 0 ? 0x3214u : l % 4 == 1 ? 0x3240u : l % 4 == 2 ? 0x3410u : 0x4210u;
-        X[l / 4] = __byte_perm(X[l / 4], xl, sel);                  // byte l%4 <- low byte of xl
-        // 2^52 + r is exact in the low word of a double with exponent 2^52; subtracting 2^52 + floor(m/2) leaves x_l
-        d[l] = __hiloint2double(0x43300000, (int)r) - (4503599627370496.0 + (double)half_of(l));
-        (void)m;
-    });
-    double y = d[NM - 1];
 #pragma unroll
-    for (int l = NM - 2; l >= 0; l--) y = fma(y, (double)modulus(l), d[l]);
+            for (int e = 0; e < E; e++) acc[e] = dp4a_ss(X[e][g], cw, acc[e]);
+        });
+        constexpr uint32_t sel = l % 4 == 0 ? 0x3214u : l % 4 == 1 ? 0x3240u : l % 4 == 2 ? 0x3410u : 0x4210u;
+#pragma unroll
+        for (int e = 0; e < E; e++) {
+            const uint32_t xl = mod_magic<l>((uint32_t)acc[e]) - (uint32_t)half_of(l);   // balanced digit, low byte
+            X[e][l / 4] = __byte_perm(X[e][l / 4], xl, sel);                             // byte l%4 <- xl
+        }
+    });
+}
+
+// digit l of a packed word as a double: sign-extend the byte (one permute), then the 2^52 + 2^31 trick (one xor, one add)
+template <int B>
+__device__ __forceinline__ double digit_to_double(uint32_t word) {
+    constexpr uint32_t sel = B == 0 ? 0x8880u : B == 1 ? 0x9991u : B == 2 ? 0xAAA2u : 0xBBB3u;   // byte B, sign-replicated above it
+    uint32_t v;   // prmt: bit 3 of a selector nibble replicates the sign bit of the selected byte over the whole result byte
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(v) : "r"(word), "r"(0u), "r"(sel));
+    v ^= 0x80000000u;
+    return __hiloint2double(0x43300000, (int)v) - 4503601774854144.0;                            // 2^52 + 2^31
+}
+
+// the reference's Horner loop (src/ozaki2.cuh:93-95) on the packed digits of one element
+template <int NM>
+__device__ __forceinline__ double horner(const uint32_t (&X)[(NM + 3) / 4]) {
+    double y = digit_to_double<(NM - 1) % 4>(X[(NM - 1) / 4]);
+    static_for<1, NM>([&](auto I) {
+        constexpr int l = NM - 1 - decltype(I)::value;
+        y = fma(y, (double)modulus(l), digit_to_double<l % 4>(X[l / 4]));
+    });
     return y;
 }
 
@@ -111,13 +131,11 @@ __global__ void __launch_bounds__(256) crt_kernel(const In *__restrict__ Cp, siz
             }
         }
     }
+    garner_digits<NM, 4>(E);
     const int si = sa[i];
     double out[4];
 #pragma unroll
-    for (int e = 0; e < 4; e++) {
-        const double y = garner_horner<NM>(E[e]);
-        out[e] = j0 + e < N ? unscale(y, -(si + sb[j0 + e])) : 0.0;
-    }
+    for (int e = 0; e < 4; e++) out[e] = j0 + e < N ? unscale(horner<NM>(E[e]), -(si + sb[j0 + e])) : 0.0;
     double *dst = C + (size_t)i * ldc + j0;
     if (j0 + 3 < N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
         reinterpret_cast<double2 *>(dst)[0] = make_double2(out[0], out[1]);

@@ -136,6 +136,46 @@ __device__ __forceinline__ void decode_work(const Params &p, int w, int &z, int 
     tn = within / rows;
 }
 
+// the epilogue of one 32-column piece of one accumulator row: shared by both kernels
+template <bool FUSED_MOD>
+__device__ __forceinline__ void store_piece(const Params &p, const ModConsts &mc, const uint32_t (&v)[32], int z, int row, int col) {
+    if (row >= p.M || col >= p.N) return;
+    if constexpr (FUSED_MOD) {
+        int8_t *dst = reinterpret_cast<int8_t *>(p.C) + (size_t)z * p.plane_c + (size_t)row * p.ldc + col;
+        uint32_t prev[8] = {};
+        if (p.accumulate) {   // residues of the K chunks before this one: residues add, |sum| stays far below 2^31
+            if (col + 16 <= p.ldc) { const uint4 q = *reinterpret_cast<const uint4 *>(dst); prev[0] = q.x; prev[1] = q.y; prev[2] = q.z; prev[3] = q.w; }
+            if (col + 32 <= p.ldc) { const uint4 q = *reinterpret_cast<const uint4 *>(dst + 16); prev[4] = q.x; prev[5] = q.y; prev[6] = q.z; prev[7] = q.w; }
+        }
+        uint32_t o[8];
+#pragma unroll
+        for (int g = 0; g < 8; g++) {
+            uint32_t x[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int add = (int)(int8_t)(prev[g] >> (8 * e));
+                const uint32_t u = (v[4 * g + e] + (uint32_t)add) ^ 0x80000000u;   // product (+ earlier chunks) + 2^31, non-negative
+                const uint32_t t = (u >> 16) * mc.c16 + (u & 0xFFFFu) + mc.adj;  // same class mod m, below 2^24 + 2^16
+                x[e] = t - __umulhi(t, mc.magic) * mc.m - (uint32_t)mc.half;     // balanced residue
+            }
+            o[g] = pack_low_bytes(x[0], x[1], x[2], x[3]);
+        }
+        if (col + 16 <= p.ldc) *reinterpret_cast<uint4 *>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
+        if (col + 32 <= p.ldc) *reinterpret_cast<uint4 *>(dst + 16) = make_uint4(o[4], o[5], o[6], o[7]);
+    } else {
+        int32_t *dst = reinterpret_cast<int32_t *>(p.C) + (size_t)z * p.plane_c + (size_t)row * p.ldc + col;
+        if (col + 32 <= p.N && ((p.ldc | p.plane_c) & 3) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0) {
+#pragma unroll
+            for (int g = 0; g < 8; g++)
+                reinterpret_cast<uint4 *>(dst)[g] = make_uint4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 32; e++)
+                if (col + e < p.N) dst[e] = (int32_t)v[e];
+        }
+    }
+}
+
 template <bool FUSED_MOD>
 __global__ void __launch_bounds__(THREADS, 1) gemm_i8_tc(const __grid_constant__ CUtensorMap mapA,
                                                          const __grid_constant__ CUtensorMap mapB, const Params p) {
@@ -229,38 +269,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_i8_tc(const __grid_constant__
                 uint32_t v[32];
                 tmem_ld32(taddr + c * 32, v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                const int col = tn * BN + c * 32;
-                if (row < p.M && col < p.N) {
-                    if constexpr (FUSED_MOD) {
-                        uint32_t o[8];
-#pragma unroll
-                        for (int g = 0; g < 8; g++) {
-                            uint32_t x[4];
-#pragma unroll
-                            for (int e = 0; e < 4; e++) {
-                                const uint32_t u = v[4 * g + e] ^ 0x80000000u;                 // product + 2^31, non-negative
-                                const uint32_t t = (u >> 16) * mc.c16 + (u & 0xFFFFu) + mc.adj;  // same class mod m, below 2^24 + 2^16
-                                x[e] = t - __umulhi(t, mc.magic) * mc.m - (uint32_t)mc.half;     // balanced residue
-                            }
-                            o[g] = pack_low_bytes(x[0], x[1], x[2], x[3]);
-                        }
-                        int8_t *dst = reinterpret_cast<int8_t *>(p.C) + (size_t)z * p.plane_c + (size_t)row * p.ldc + col;
-                        // ldc is a multiple of 16 and the planes are padded to it: 16-byte pieces never leave the row
-                        if (col + 16 <= p.ldc) *reinterpret_cast<uint4 *>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
-                        if (col + 32 <= p.ldc) *reinterpret_cast<uint4 *>(dst + 16) = make_uint4(o[4], o[5], o[6], o[7]);
-                    } else {
-                        int32_t *dst = reinterpret_cast<int32_t *>(p.C) + (size_t)z * p.plane_c + (size_t)row * p.ldc + col;
-                        if (col + 32 <= p.N && ((p.ldc | p.plane_c) & 3) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0) {
-#pragma unroll
-                            for (int g = 0; g < 8; g++)
-                                reinterpret_cast<uint4 *>(dst)[g] = make_uint4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
-                        } else {
-#pragma unroll
-                            for (int e = 0; e < 32; e++)
-                                if (col + e < p.N) dst[e] = (int32_t)v[e];
-                        }
-                    }
-                }
+                store_piece<FUSED_MOD>(p, mc, v, z, row, tn * BN + c * 32);
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -340,46 +349,6 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t bar) {   // bar: a barr
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-
-// the epilogue of one 32-column piece of one accumulator row: shared by both kernels
-template <bool FUSED_MOD>
-__device__ __forceinline__ void store_piece(const Params &p, const ModConsts &mc, const uint32_t (&v)[32], int z, int row, int col) {
-    if (row >= p.M || col >= p.N) return;
-    if constexpr (FUSED_MOD) {
-        int8_t *dst = reinterpret_cast<int8_t *>(p.C) + (size_t)z * p.plane_c + (size_t)row * p.ldc + col;
-        uint32_t prev[8] = {};
-        if (p.accumulate) {   // residues of the K chunks before this one: residues add, |sum| stays far below 2^31
-            if (col + 16 <= p.ldc) { const uint4 q = *reinterpret_cast<const uint4 *>(dst); prev[0] = q.x; prev[1] = q.y; prev[2] = q.z; prev[3] = q.w; }
-            if (col + 32 <= p.ldc) { const uint4 q = *reinterpret_cast<const uint4 *>(dst + 16); prev[4] = q.x; prev[5] = q.y; prev[6] = q.z; prev[7] = q.w; }
-        }
-        uint32_t o[8];
-#pragma unroll
-        for (int g = 0; g < 8; g++) {
-            uint32_t x[4];
-#pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const int add = (int)(int8_t)(prev[g] >> (8 * e));
-                const uint32_t u = (v[4 * g + e] + (uint32_t)add) ^ 0x80000000u;   // product (+ earlier chunks) + 2^31, non-negative
-                const uint32_t t = (u >> 16) * mc.c16 + (u & 0xFFFFu) + mc.adj;  // same class mod m, below 2^24 + 2^16
-                x[e] = t - __umulhi(t, mc.magic) * mc.m - (uint32_t)mc.half;     // balanced residue
-            }
-            o[g] = pack_low_bytes(x[0], x[1], x[2], x[3]);
-        }
-        if (col + 16 <= p.ldc) *reinterpret_cast<uint4 *>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
-        if (col + 32 <= p.ldc) *reinterpret_cast<uint4 *>(dst + 16) = make_uint4(o[4], o[5], o[6], o[7]);
-    } else {
-        int32_t *dst = reinterpret_cast<int32_t *>(p.C) + (size_t)z * p.plane_c + (size_t)row * p.ldc + col;
-        if (col + 32 <= p.N && ((p.ldc | p.plane_c) & 3) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0) {
-#pragma unroll
-            for (int g = 0; g < 8; g++)
-                reinterpret_cast<uint4 *>(dst)[g] = make_uint4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
-        } else {
-#pragma unroll
-            for (int e = 0; e < 32; e++)
-                if (col + e < p.N) dst[e] = (int32_t)v[e];
-        }
-    }
 }
 
 template <bool FUSED_MOD>

@@ -115,6 +115,36 @@ OZ_HD constexpr uint64_t epi_umax(int l) {
     return 65535ull * c.c16 + 65535ull + c.adj;
 }
 
+// Tables of the double-double path's direct-sum CRT (reference: src/ozaki_dd.cuh:73-91, crt_consts): for the first NM
+// moduli with product P, W[l] = (P/m_l) * ((P/m_l)^-1 mod m_l) and P as eight 32-bit limbs, F[l] = round(2^40 w_l / m_l).
+template <int NM>
+struct DdTables {
+    unsigned W[NM][8];
+    unsigned P[8];
+    long long F[NM];
+};
+OZ_HD constexpr void mul_small(unsigned (&a)[8], unsigned m) {
+    unsigned long long c = 0;
+    for (int k = 0; k < 8; k++) { c += (unsigned long long)a[k] * m; a[k] = (unsigned)c; c >>= 32; }
+}
+template <int NM>
+OZ_HD constexpr DdTables<NM> make_dd_tables() {
+    DdTables<NM> t{};
+    t.P[0] = 1;
+    for (int l = 0; l < NM; l++) mul_small(t.P, (unsigned)modulus(l));
+    for (int l = 0; l < NM; l++) {
+        const int ml = modulus(l);
+        int r = 1;
+        t.W[l][0] = 1;
+        for (int s = 0; s < NM; s++)
+            if (s != l) { mul_small(t.W[l], (unsigned)modulus(s)); r = r * (modulus(s) % ml) % ml; }
+        const int w = inv_mod_c(r, ml);
+        mul_small(t.W[l], (unsigned)w);
+        // llround(ldexp((double)w / m, 40)): the quotient has 13 spare bits below 2^40, so adding 0.5 is exact
+        t.F[l] = (long long)((double)w / ml * 1099511627776.0 + 0.5);
+    }
+    return t;
+}
 template <int L, int N, class F>
 OZ_HD inline void static_for(F &&f) {
     if constexpr (L < N) {

@@ -36,3 +36,17 @@ def digest(*arrays):
     for a in arrays:
         h.update(np.ascontiguousarray(a).tobytes())
     return h.hexdigest()
+
+
+# double-double cases: name -> (M, N, K, seed); 32 moduli (the reference's C ABI fixes that count)
+DD_CASES = {"dd_cfg": (128, 128, 256, 20), "dd_odd": (77, 130, 515, 21)}
+
+
+def dd_inputs(name):
+    M, N, K, seed = DD_CASES[name]
+    rng = np.random.default_rng(2000 + seed)
+    Ah = np.ldexp(rng.uniform(-1.0, 1.0, (M, K)), rng.integers(-8, 9, (M, K)).astype(np.int32))
+    Bh = np.ldexp(rng.uniform(-1.0, 1.0, (K, N)), rng.integers(-8, 9, (K, N)).astype(np.int32))
+    Al = Ah * 2.0**-53 * rng.uniform(-1.0, 1.0, (M, K))
+    Bl = Bh * 2.0**-53 * rng.uniform(-1.0, 1.0, (K, N))
+    return [np.ascontiguousarray(x) for x in (Ah, Al, Bh, Bl)]

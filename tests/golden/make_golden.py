@@ -35,6 +35,18 @@ def main():
         store[name + ".C"] = C.view(np.uint64)
         store[name + ".inputs_sha256"] = np.array(cases.digest(A, B))
         print(name, C.shape, "ok")
+    ref.ozb_ddgemm.argtypes = [ctypes.c_int] * 3 + [ctypes.c_void_p] * 6 + [ctypes.c_int]
+    for name in cases.DD_CASES:
+        Ah, Al, Bh, Bl = cases.dd_inputs(name)
+        M, K = Ah.shape
+        N = Bh.shape[1]
+        Ch, Cl = np.full((M, N), np.nan), np.full((M, N), np.nan)
+        rc = ref.ozb_ddgemm(M, N, K, Ah.ctypes.data, Al.ctypes.data, Bh.ctypes.data, Bl.ctypes.data, Ch.ctypes.data, Cl.ctypes.data, 1)
+        if rc:
+            raise RuntimeError(f"{name}: reference ozb_ddgemm returned {rc}: {ref.ozb_error(rc).decode()}")
+        store[name + ".Ch"], store[name + ".Cl"] = Ch.view(np.uint64), Cl.view(np.uint64)
+        store[name + ".inputs_sha256"] = np.array(cases.digest(Ah, Al, Bh, Bl))
+        print(name, Ch.shape, "ok")
     ref.ozb_release()
     np.savez_compressed(out, **store)
     print("wrote", out, os.path.getsize(out), "bytes")

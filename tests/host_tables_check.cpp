@@ -105,9 +105,67 @@ template <int NM> static long check_garner(std::mt19937_64 &g) {
     return bad;
 }
 
+// ---- double-double path ----
+//   4. residue of V = u 2^53 + t from the sixteen bytes of (u + 2^62, t + 2^62)   (dd.cu: residues_of_4_dd)
+//   5. the direct-sum CRT tables: known signed integers of up to 192 bits come back from their residues
+//      (the reference's own known-answer test, bench/crt_check.cpp:18-35)
+template <int L> static int dd_residue(long long u, long long t) {
+    constexpr int l = L, m = modulus(l), p53 = pow2_mod(53, m);
+    if (l == 0) return (int)(int8_t)(t & 255);
+    int wt[8], wu[8];
+    for (int i = 0; i < 8; i++) { wt[i] = byte_weight(i, l); wu[i] = bal_c((long long)posmod_c(byte_weight(i, l), m) * p53, m); }
+    constexpr int bound = 16 * 255 * 128;
+    constexpr int off = posmod_c((long long)pow2_mod(62, m) * p53 + pow2_mod(62, m), m);
+    constexpr int init = lift_of(l, bound) - off;
+    static_assert(init > bound && magic_ok(l, (uint64_t)init + bound), "range");
+    const uint64_t a = (uint64_t)u + (1ull << 62), b = (uint64_t)t + (1ull << 62);
+    int acc = init;
+    acc = dp4a((uint32_t)b, pack4(wt[0], wt[1], wt[2], wt[3]), acc, false);
+    acc = dp4a((uint32_t)(b >> 32), pack4(wt[4], wt[5], wt[6], wt[7]), acc, false);
+    acc = dp4a((uint32_t)a, pack4(wu[0], wu[1], wu[2], wu[3]), acc, false);
+    acc = dp4a((uint32_t)(a >> 32), pack4(wu[4], wu[5], wu[6], wu[7]), acc, false);
+    const uint32_t uu = (uint32_t)acc;
+    return (int)(int8_t)((uu - umulhi(uu, magic_of(l)) * (uint32_t)m - (uint32_t)half_of(l)) & 255);
+}
+template <int L> static long check_dd_mod(std::mt19937_64 &g) {
+    long bad = 0;
+    constexpr int m = modulus(L);
+    for (int i = 0; i < 20000; i++) {
+        long long u = (long long)(g() >> 11) - (1ll << 52), t = (long long)(g() >> 9) - (1ll << 54);
+        if (i < 4) { u = i & 1 ? (1ll << 53) - 1 : -(1ll << 53) + 1; t = i & 2 ? (1ll << 55) : -(1ll << 55); }
+        const __int128 V = (__int128)u * ((__int128)1 << 53) + t;
+        int r = (int)(V % m); if (r < 0) r += m; if (r >= (m + 1) / 2) r -= m;
+        bad += dd_residue<L>(u, t) != r;
+    }
+    return bad;
+}
+template <int NM> static long check_dd_crt(std::mt19937_64 &g) {
+    constexpr DdTables<NM> T = make_dd_tables<NM>();
+    long bad = 0;
+    const int maxlimbs = NM >= 32 ? 6 : NM >= 28 ? 5 : 4;   // stay below P/2
+    for (int it = 0; it < 20000; it++) {
+        unsigned V[8] = {}; const int nl = 1 + g() % maxlimbs; for (int k = 0; k < nl; k++) V[k] = (unsigned)g();
+        const bool sgn = g() & 1;
+        if (sgn) { unsigned long long b = 1; for (int k = 0; k < 8; k++) { b += (unsigned)~V[k]; V[k] = (unsigned)b; b >>= 32; } }
+        unsigned long long acc[8] = {}; long long qf = 0;
+        for (int l = 0; l < NM; l++) {
+            const int m = modulus(l);
+            long long x = 0; for (int k = 7; k >= 0; k--) x = ((x << 32) + V[k]) % m;
+            if (sgn) { long long p = 1; for (int t = 0; t < 256; t++) p = p * 2 % m; x = ((x - p) % m + m) % m; }
+            qf += x * T.F[l]; for (int k = 0; k < 8; k++) acc[k] += (unsigned long long)x * T.W[l][k];
+        }
+        long long q = (qf + (1ll << 39)) >> 40, c = 0; bool same = true;
+        for (int k = 0; k < 8; k++) { c += (long long)acc[k] - q * (long long)T.P[k]; same &= (unsigned)c == V[k]; c >>= 32; }
+        bad += !same;
+    }
+    return bad;
+}
+
 int main() {
     std::mt19937_64 g(12345);
     long bad = 0;
+    static_for<0, 32>([&](auto L) { bad += check_dd_mod<decltype(L)::value>(g); });
+    bad += check_dd_crt<24>(g) + check_dd_crt<28>(g) + check_dd_crt<32>(g);
     static_for<0, MAXM>([&](auto L) { bad += check_mod<decltype(L)::value>(g); });
     static_for<8, 17>([&](auto N) { bad += check_garner<decltype(N)::value>(g); });
     printf("%ld wrong\n", bad);

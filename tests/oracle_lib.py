@@ -151,3 +151,79 @@ def ref_fill(n, spread, seed):
     v = np.empty(n, dtype=np.float64)
     lib.oz_ref_fill(_ptr(v), n, float(spread), seed)
     return v
+
+
+# ---- double-double path (oracle/ozaki_dd_oracle.c) ----
+_i, _ll, _d, _p, _sz = ctypes.c_int, ctypes.c_longlong, ctypes.c_double, ctypes.c_void_p, ctypes.c_size_t
+lib.oz_oracle_residues_dd.argtypes = [_p, _p, _i, _i, _ll, _ll, _p, _i, _p, _i, _sz]
+lib.oz_oracle_residues_dd.restype = None
+lib.oz_oracle_crt_dd.argtypes = [_p, _sz, _i, _i, _i, _p, _p, _i, _p, _p, _i, _i]
+lib.oz_oracle_crt_dd.restype = None
+lib.oz_oracle_ddgemm.argtypes = [_i, _i, _i, _p, _p, _p, _p, _p, _p, _i, _i]
+lib.oz_oracle_ref_quad.argtypes = [_p, _p, _p, _p, _i, _i, _i, _p, _p, _p]
+lib.oz_oracle_ref_quad.restype = None
+lib.oz_oracle_dd_err_units.argtypes = [_p, _p, _p, _p, _p, _sz]
+lib.oz_oracle_dd_err_units.restype = _d
+lib.oz_oracle_dd_crt_kat.argtypes = [_p, _i, _i]
+lib.oz_ref_fill_dd.argtypes = [_p, _p, _sz, _p, _p, _sz, _d, ctypes.c_uint]
+lib.oz_ref_fill_dd.restype = None
+
+
+def _c(a, dt=np.float64):
+    return np.ascontiguousarray(a, dtype=dt)
+
+
+def residues_dd(Xh, Xl, rows, length, s_row, s_col, s, nm, ld=None):
+    Xh, Xl, s = _c(Xh), _c(Xl), _c(s, np.int32)
+    ld = length if ld is None else ld
+    R = np.zeros((nm, rows, ld), dtype=np.int8)
+    lib.oz_oracle_residues_dd(_ptr(Xh), _ptr(Xl), rows, length, s_row, s_col, _ptr(s), nm, _ptr(R), ld, rows * ld)
+    return R
+
+
+def crt_dd(Cl, sa, sb, mode=0, Ch=None, Cl_=None):
+    Cl = _c(Cl, np.int32)
+    nm, M, N = Cl.shape
+    sa, sb = _c(sa, np.int32), _c(sb, np.int32)
+    Ch = np.zeros((M, N)) if Ch is None else _c(Ch).copy()
+    Cl_ = np.zeros((M, N)) if Cl_ is None else _c(Cl_).copy()
+    lib.oz_oracle_crt_dd(_ptr(Cl), M * N, M, N, N, _ptr(sa), _ptr(sb), nm, _ptr(Ch), _ptr(Cl_), N, mode)
+    return Ch, Cl_
+
+
+def ddgemm(Ah, Al, Bh, Bl, nm=32, mode=0, Ch=None, Cl=None):
+    Ah, Al, Bh, Bl = _c(Ah), _c(Al), _c(Bh), _c(Bl)
+    M, K = Ah.shape
+    N = Bh.shape[1]
+    Ch = np.zeros((M, N)) if Ch is None else _c(Ch).copy()
+    Cl = np.zeros((M, N)) if Cl is None else _c(Cl).copy()
+    rc = lib.oz_oracle_ddgemm(M, N, K, _ptr(Ah), _ptr(Al), _ptr(Bh), _ptr(Bl), _ptr(Ch), _ptr(Cl), nm, mode)
+    if rc:
+        raise RuntimeError(f"oracle ddgemm failed: {rc}")
+    return Ch, Cl
+
+
+def ref_quad(Ah, Al, Bh, Bl):
+    Ah, Al, Bh, Bl = _c(Ah), _c(Al), _c(Bh), _c(Bl)
+    M, K = Ah.shape
+    N = Bh.shape[1]
+    Rh, Rl, Ab = np.empty((M, N)), np.empty((M, N)), np.empty((M, N))
+    lib.oz_oracle_ref_quad(_ptr(Ah), _ptr(Al), _ptr(Bh), _ptr(Bl), M, N, K, _ptr(Rh), _ptr(Rl), _ptr(Ab))
+    return Rh, Rl, Ab
+
+
+def dd_err_units(Ch, Cl, Rh, Rl, Ab):
+    Ch, Cl, Rh, Rl, Ab = _c(Ch), _c(Cl), _c(Rh), _c(Rl), _c(Ab)
+    return lib.oz_oracle_dd_err_units(_ptr(Ch), _ptr(Cl), _ptr(Rh), _ptr(Rl), _ptr(Ab), Ch.size)
+
+
+def dd_crt_kat(V, nm=32):
+    V = np.ascontiguousarray(V, dtype=np.uint32)
+    return lib.oz_oracle_dd_crt_kat(_ptr(V), V.shape[0], nm)
+
+
+def ref_fill_dd(M, N, K, spread):
+    Ah, Al = np.empty(M * K), np.empty(M * K)
+    Bh, Bl = np.empty(K * N), np.empty(K * N)
+    lib.oz_ref_fill_dd(_ptr(Ah), _ptr(Al), M * K, _ptr(Bh), _ptr(Bl), K * N, float(spread), K + int(spread))
+    return Ah.reshape(M, K), Al.reshape(M, K), Bh.reshape(K, N), Bl.reshape(K, N)

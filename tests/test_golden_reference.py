@@ -38,3 +38,30 @@ def test_library_equals_reference_output(name):
     A, B, nm, want = _load(name)
     got = g.gpu_dgemm(A, B, nm).view(np.uint64)
     assert np.array_equal(got, want), f"{(got != want).sum()} of {got.size} entries differ from the reference's output"
+
+
+def _load_dd(name):
+    z = np.load(GOLDEN)
+    if name + ".Ch" not in z:
+        pytest.skip("golden file predates the double-double cases")
+    parts = cases.dd_inputs(name)
+    assert str(z[name + ".inputs_sha256"]) == cases.digest(*parts)
+    return parts, z[name + ".Ch"], z[name + ".Cl"]
+
+
+@needs_golden
+@pytest.mark.parametrize("name", sorted(cases.DD_CASES))
+def test_dd_checker_equals_reference_output(name):
+    (Ah, Al, Bh, Bl), wh, wl = _load_dd(name)
+    Ch, Cl = o.ddgemm(Ah, Al, Bh, Bl, 32)
+    assert np.array_equal(Ch.view(np.uint64), wh) and np.array_equal(Cl.view(np.uint64), wl)
+
+
+@needs_golden
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", sorted(cases.DD_CASES))
+def test_dd_library_equals_reference_output(name):
+    import test_gpu_dd
+    (Ah, Al, Bh, Bl), wh, wl = _load_dd(name)
+    Ch, Cl = test_gpu_dd._gpu_ddgemm(Ah, Al, Bh, Bl)
+    assert np.array_equal(Ch.view(np.uint64), wh) and np.array_equal(Cl.view(np.uint64), wl)
