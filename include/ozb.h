@@ -115,6 +115,16 @@ int ozb_dgemm_ex(int M, int N, int K, const double *A, long long lda, const doub
 int ozb_ddgemm_ex(int M, int N, int K, const double *Ah, const double *Al, long long lda, const double *Bh, const double *Bl,
                   long long ldb, double *Ch, double *Cl, long long ldo, int moduli, int mode, void *stream);
 
+/* llm/tgemm.cu:61-162 (the reference's tiled exact product, F8 mode) checked as the reference checks it, against the
+ * exact sum rounded once (llm/ultra.cu:336-369) -- Y = RN_fp32(X (W o S)): X is M x K bf16 (uint16 bit patterns), W is
+ * K x N FP8 E4M3 bytes, S holds one FP32 scale per 128 x 128 block of W ([ceil(K/128)][ceil(N/128)]), Y is M x N FP32;
+ * all dense row-major device pointers. Every output is the round-to-nearest-even FP32 value of the exact sum. Operands
+ * whose exponents span more than the 62-bit windows are truncated; an output whose rounding that leaves undecided is
+ * returned as NaN and counted in *open (0 for ordinary data). *moduli receives the number of INT8 GEMM planes used
+ * (8..19, chosen from the data). Synchronous. Non-finite inputs give OZB_EARG. */
+int ozb_bf16_fp8_gemm(int M, int N, int K, const void *X, const void *W, const float *S, float *Y, int *open, int *moduli,
+                      void *stream);
+
 /* The four stages on caller-owned device buffers (what bench/phases.cu launches one by one). Asynchronous.
  * Pitches: ld of int8 planes in bytes and a multiple of 16; `plane` = distance between planes in elements. */
 /* src/ozaki2.cuh:56-78 -- scales + residues of an A-like operand (rows of `len` contiguous doubles, pitch ldx) */

@@ -422,6 +422,7 @@ OZB_API int ozb_tdgemm(int M, int N, int K, const double *, const double *, cons
 OZB_API void ozb_release(void) {
     std::lock_guard<std::mutex> g(mu);
     for (Cache &c : cache) if (c.p) { plan_free(c.p); c.p = nullptr; }
+    exact_f8_release();
 }
 
 static int bench_dd(int n, int reps, double *median_ms) {   // python/capi.cu:130-164, kind 1: lower parts 2^-53 below
@@ -614,6 +615,12 @@ OZB_API int ozb_crt_i8(int moduli, const int8_t *Cr, size_t plane, int M, int N,
         (reinterpret_cast<uintptr_t>(Cr) & 3) || ldc < N)
         return OZB_EARG;
     return (int)crt_from_i8(moduli, Cr, plane, M, N, ldr, sa, sb, C, ldc, (cudaStream_t)stream);
+}
+OZB_API int ozb_bf16_fp8_gemm(int M, int N, int K, const void *X, const void *W, const float *S, float *Y, int *open, int *moduli, void *stream) {
+    if (int e = check_args(M, N, K)) return e;
+    if (!X || !W || !S || !Y) return OZB_EARG;
+    std::lock_guard<std::mutex> g(mu);
+    return exact_bf16_fp8_gemm(M, N, K, (const uint16_t *)X, K, (const uint8_t *)W, N, S, Y, N, open, moduli, (cudaStream_t)stream);
 }
 OZB_API int ozb_int8_peak(int iters, int pair, float *ms, double *tops) {
     if (int e = check_args(1, 1, 1)) return e;

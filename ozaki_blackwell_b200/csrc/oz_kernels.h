@@ -27,4 +27,9 @@ cudaError_t dd_scale_residues_cols(int nm, const double *Xh, const double *Xl, i
 cudaError_t dd_crt_from_i8(int nm, const int8_t *Cr, size_t plane, int M, int N, long long ldr, const int *sa, const int *sb, double *Ch,
                            double *Cl, long long ldo, int mode, cudaStream_t st);
 
+// correctly rounded BF16 x block-scaled FP8 product (exact_f8.cu)
+int exact_bf16_fp8_gemm(int M, int N, int K, const uint16_t *X, long long ldx, const uint8_t *W, long long ldw, const float *S, float *Y,
+                        long long ldy, int *open, int *moduli, cudaStream_t st);
+void exact_f8_release();
+
 }  // namespace ozk
