@@ -23,7 +23,7 @@ using namespace ozk;
 // ---------------------------------------------------------------------------------------------------------------
 // plan
 // ---------------------------------------------------------------------------------------------------------------
-constexpr int HOST_PANELS = 8;
+constexpr int HOST_PANELS = 32;
 struct ozb_plan {
     int M, N, K, nm, bits, maxbits;
     int Kp, Np;                      // pitch of the residue planes of A and B (bytes); pitch of the product planes (bytes)
@@ -143,13 +143,14 @@ static int plan_make(int M, int N, int K, int nm, int maxbits, ozb_plan **out) {
 // The fused GEMMs of one column panel. A long K is cut into chunks of about 8192: within one chunk the A band and the B
 // panels that the resident CTAs share fit the L2 cache, whereas at K = 32768 they do not (measured: 1.8 instead of 3.2
 // POP/s, the kernel turns HBM-bound); later chunks add to the residues the earlier ones stored.
-static cudaError_t gemm_chunks(ozb_plan *p, const int8_t *Br, int8_t *Cr, int n, cudaStream_t st) {
+static cudaError_t gemm_chunks(ozb_plan *p, const int8_t *Br, int8_t *Cr, int n, cudaStream_t st, int i0 = 0, int m = -1) {
+    if (m < 0) m = p->M;   // rows [i0, i0 + m) of A and C
     const int chunks = p->K > 12288 ? (p->K + 8191) / 8192 : 1;
     const int kc = round_up((p->K + chunks - 1) / chunks, 128);
     for (int k0 = 0, i = 0; k0 < p->K; k0 += kc, i++) {
         const int klen = p->K - k0 < kc ? p->K - k0 : kc;
-        cudaError_t e = gemm_i8_planes(p->Ar + k0, Br + k0, Cr, p->M, n, klen, p->nm, p->Kp, p->Kp, p->Np, p->planeA, p->planeB,
-                                       p->planeC, 1, 0, p->status, 0, st, i > 0);
+        cudaError_t e = gemm_i8_planes(p->Ar + (size_t)i0 * p->Kp + k0, Br + k0, Cr + (size_t)i0 * p->Np, m, n, klen, p->nm, p->Kp, p->Kp,
+                                       p->Np, p->planeA, p->planeB, p->planeC, 1, 0, p->status, 0, st, i > 0);
         if (e) return e;
     }
     return cudaSuccess;
@@ -228,11 +229,13 @@ static int plan_ddgemm(ozb_plan *p, const double *Ah, const double *Al, long lon
     return (int)e;
 }
 
-// Host operands (python/capi.cu:37-48,82-88 stage everything, compute, copy back). Here the three phases overlap: A goes
-// first, then B in column panels; each panel is scaled, multiplied and reconstructed as soon as it has landed, and its
-// columns of C travel back while the next panel is being computed. With pinned host memory the copies are asynchronous
-// and the product hides behind the transfer of B; with pageable memory the calls below block in issue order and the
-// result is the same. The device copies stay with the plan (freed by ozb_release).
+// Host operands (python/capi.cu:37-48,82-88 stage everything, compute, copy back). Here the three phases overlap and every
+// copy is contiguous: B goes first, in chunks of rows whose column maxima are taken as they land; once B is complete its
+// residues are formed, and A follows in blocks of rows. A block of rows of C needs only its rows of A (row scales are
+// local), so each block is scaled, multiplied and reconstructed as soon as it has landed, and its rows of C travel back
+// while the next block is in flight. With pinned host memory the copies are asynchronous and the whole product hides
+// behind the transfers; with pageable memory the calls below block in issue order and the result is the same.
+// The device copies stay with the plan (freed by ozb_release).
 static int plan_dgemm_host(ozb_plan *p, const double *A, const double *B, double *C) {
     const size_t M = p->M, N = p->N, K = p->K;
     cudaError_t e = cudaSuccess;
@@ -247,28 +250,43 @@ static int plan_dgemm_host(ozb_plan *p, const double *A, const double *B, double
         for (auto &ev : p->evRun) if (!e) e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
         if (e) return (int)e;
     }
-    int panels = (p->N + 1023) / 1024;           // about 1024 columns each, starts on multiples of 256
-    if (panels > HOST_PANELS) panels = HOST_PANELS;
-    if (panels < 1) panels = 1;
-    const int width = round_up((p->N + panels - 1) / panels, 256);
-    panels = (p->N + width - 1) / width;
-    e = cudaMemcpyAsync(p->hA, A, M * K * 8, cudaMemcpyHostToDevice, p->sIn);
-    if (!e) e = cudaEventRecord(p->evIn[0], p->sIn);
-    if (!e) e = cudaStreamWaitEvent(p->sRun, p->evIn[0], 0);
-    if (!e) e = (cudaError_t)plan_set_a(p, p->hA, (long long)K, p->sRun);
-    for (int q = 0; q < panels && !e; q++) {
-        const int j0 = q * width, n = (p->N - j0 < width) ? p->N - j0 : width;
-        e = cudaMemcpy2DAsync(p->hB + j0, N * 8, B + j0, N * 8, (size_t)n * 8, K, cudaMemcpyHostToDevice, p->sIn);
-        if (!e) e = cudaEventRecord(p->evIn[q + 1], p->sIn);
-        if (!e) e = cudaStreamWaitEvent(p->sRun, p->evIn[q + 1], 0);
-        if (!e) e = (cudaError_t)plan_panel(p, p->hB + j0, (long long)N, p->hC + j0, (long long)N, j0, n, p->sRun, nullptr);
+    static const int want = [] { const char *env = getenv("OZ_HOST_PANELS"); return env && *env ? atoi(env) : 0; }();
+    auto pieces = [&](size_t extent) {   // about 512 rows per piece, at most 16 (measured on B200: 16 beats 8 and 4 at n = 8192)
+        int n = want > 0 ? want : (int)(extent / 512);
+        if (n > 16) n = 16;
+        if (n > HOST_PANELS) n = HOST_PANELS;
+        return n < 1 ? 1 : n;
+    };
+    const int blocks = pieces(M) > pieces(K) ? pieces(M) : pieces(K);
+    const int kchunk = (int)((K + pieces(K) - 1) / pieces(K)), mblock = (int)((M + pieces(M) - 1) / pieces(M));
+    p->last = p->sRun;
+    e = cudaMemsetAsync(p->colmax, 0, N * 8, p->sRun);
+    for (int q = 0; q < blocks && !e; q++) {   // B, chunk of rows by chunk
+        const size_t k0 = (size_t)q * kchunk;
+        if (k0 >= K) break;
+        const int rows = (int)(K - k0 < (size_t)kchunk ? K - k0 : kchunk);
+        e = cudaMemcpyAsync(p->hB + k0 * N, B + k0 * N, (size_t)rows * N * 8, cudaMemcpyHostToDevice, p->sIn);
+        if (!e) e = cudaEventRecord(p->evIn[q], p->sIn);
+        if (!e) e = cudaStreamWaitEvent(p->sRun, p->evIn[q], 0);
+        if (!e) e = cols_absmax_accumulate(p->hB + k0 * N, rows, (int)N, (long long)N, p->colmax, p->sRun);
+    }
+    if (!e) e = cols_residues_from_max(p->nm, p->hB, (int)K, (int)N, (long long)N, p->bits, p->colmax, p->sb, p->Br, p->Kp, p->planeB, p->sRun);
+    for (int q = 0; q < blocks && !e; q++) {   // A, block of rows by block; C goes back block by block
+        const size_t i0 = (size_t)q * mblock;
+        if (i0 >= M) break;
+        const int m = (int)(M - i0 < (size_t)mblock ? M - i0 : mblock);
+        e = cudaMemcpyAsync(p->hA + i0 * K, A + i0 * K, (size_t)m * K * 8, cudaMemcpyHostToDevice, p->sIn);
+        if (!e) e = cudaEventRecord(p->evIn[q], p->sIn);
+        if (!e) e = cudaStreamWaitEvent(p->sRun, p->evIn[q], 0);
+        if (!e) e = scale_residues_rows(p->nm, p->hA + i0 * K, m, (int)K, (long long)K, p->bits, p->sa + i0, p->Ar + i0 * p->Kp, p->Kp, p->planeA, p->sRun);
+        if (!e) e = gemm_chunks(p, p->Br, p->Cr, (int)N, p->sRun, (int)i0, m);
+        if (!e) e = crt_from_i8(p->nm, p->Cr + i0 * p->Np, p->planeC, m, (int)N, p->Np, p->sa + i0, p->sb, p->hC + i0 * N, (long long)N, p->sRun);
         if (!e) e = cudaEventRecord(p->evRun[q], p->sRun);
         if (!e) e = cudaStreamWaitEvent(p->sOut, p->evRun[q], 0);
-        if (!e) e = cudaMemcpy2DAsync(C + j0, N * 8, p->hC + j0, N * 8, (size_t)n * 8, M, cudaMemcpyDeviceToHost, p->sOut);
+        if (!e) e = cudaMemcpyAsync(C + i0 * N, p->hC + i0 * N, (size_t)m * N * 8, cudaMemcpyDeviceToHost, p->sOut);
     }
     if (!e) e = cudaStreamSynchronize(p->sOut);
     cudaError_t e2 = cudaStreamSynchronize(p->sRun), e3 = cudaStreamSynchronize(p->sIn);
-    p->last = p->sRun;
     if (e) return (int)e;
     if (e2) return (int)e2;
     return (int)e3;

@@ -250,6 +250,26 @@ cudaError_t scale_residues_rows(int nm, const double *X, int rows, int len, long
                                 size_t plane, cudaStream_t st) {
     OZ_DISPATCH_NM(nm, (launch_rows_t<NM>(X, rows, len, ldx, bits, s, R, ld, plane, st)));
 }
+// The two passes of the B-like operand separately, for callers that receive the matrix in row chunks: the column maxima
+// of rows [0, rows) of X accumulate into colmax (which the caller cleared once), the residue pass runs when all chunks
+// have been seen.
+cudaError_t cols_absmax_accumulate(const double *X, int rows, int cols, long long ldx, unsigned long long *colmax, cudaStream_t st) {
+    col_absmax<<<dim3((cols + 511) / 512, (rows + CM_ROWS - 1) / CM_ROWS), 256, 0, st>>>(X, rows, cols, ldx, colmax);
+    return cudaGetLastError();
+}
+template <int NM>
+static cudaError_t launch_cols_residues_t(const double *X, int rows, int cols, long long ldx, int bits, const unsigned long long *colmax,
+                                          int *s, int8_t *R, int ld, size_t plane, cudaStream_t st) {
+    static const cudaError_t attr = cudaFuncSetAttribute(col_residues_t<NM>, cudaFuncAttributeMaxDynamicSharedMemorySize, col_tile_smem<NM>());
+    if (attr) return attr;
+    col_residues_t<NM><<<dim3((cols + CT_COLS - 1) / CT_COLS, (rows + CT_K - 1) / CT_K), 256, col_tile_smem<NM>(), st>>>(
+        X, rows, cols, ldx, colmax, bits, s, R, ld, plane);
+    return cudaGetLastError();
+}
+cudaError_t cols_residues_from_max(int nm, const double *X, int rows, int cols, long long ldx, int bits, const unsigned long long *colmax,
+                                   int *s, int8_t *R, int ld, size_t plane, cudaStream_t st) {
+    OZ_DISPATCH_NM(nm, (launch_cols_residues_t<NM>(X, rows, cols, ldx, bits, colmax, s, R, ld, plane, st)));
+}
 // B-like operand: row-major `rows` x `cols` (rows = K), scaled per column; writes s[cols] and Rt[nm][cols][ld]
 cudaError_t scale_residues_cols(int nm, const double *X, int rows, int cols, long long ldx, int bits, unsigned long long *colmax,
                                 int *s, int8_t *R, int ld, size_t plane, cudaStream_t st) {
