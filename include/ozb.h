@@ -109,6 +109,13 @@ int ozb_plan_phase_ms(ozb_plan *p, int slot, float ms[4]);
 int ozb_dgemm_ex(int M, int N, int K, const double *A, long long lda, const double *B, long long ldb, double *C,
                  long long ldc, int moduli, void *stream);
 
+/* bench/oz_strassen.cu:74-97,247 (scales_norm) -- C = A B with the reference's optional scaling from the 2-norm of each row
+ * of A and column of B instead of its largest entry (Cauchy-Schwarz bounds the integer products without K, so more bits
+ * survive: at large K one modulus fewer gives the same error). Opt-in: the result is NOT bit-identical to ozb_dgemm, it is
+ * bit-identical to the reference's pipeline run with scales_norm. Device pointers, leading dimensions, asynchronous. */
+int ozb_dgemm_norm(int M, int N, int K, const double *A, long long lda, const double *B, long long ldb, double *C, long long ldc,
+                   int moduli, void *stream);
+
 /* src/ozaki_dd.cuh:143-148 (oz::ddgemm_t) -- the double-double product with leading dimensions (elements), the
  * reference's mode (0: C = AB, 1: C -= AB, 2: C = -AB, used by its LU solvers to update blocks in place), a modulus
  * count in {24, 28, 32} and a stream; device pointers, no final synchronisation. */

@@ -233,3 +233,66 @@ void oz_oracle_fill_i8(int M, int N, int K, int8_t *A, int8_t *Bt) {
     for (size_t t = 0; t < (size_t)M * K; t++) A[t] = (int8_t)(rand() % 255 - 127);
     for (size_t t = 0; t < (size_t)N * K; t++) Bt[t] = (int8_t)(rand() % 255 - 127);
 }
+
+/* bench/oz_strassen.cu:74-97 (scales_norm) -- the optional scale from the 2-norm: s = beta - 1 - (e + ilogb(sqrt(ss)(1 + 2^-30)))
+ * with e = ilogb(max |x|) and ss = sum (x 2^-e)^2. The sum is accumulated exactly in the reference's order, because its last
+ * bits can move the result across a power of two: 256 threads, thread t takes k = t, t + 256, ... with fma; a butterfly of
+ * additions inside each warp of 32 (offsets 16, 8, 4, 2, 1); then the eight warp sums added in order. X read with strides. */
+void oz_oracle_scales_norm(const double *X, int rows, int len, long long sRow, long long sCol, int beta, int *s) {
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < rows; r++) {
+        double mx = 0;
+        for (int k = 0; k < len; k++) mx = fmax(mx, fabs(X[r * sRow + k * sCol]));
+        if (mx == 0) { s[r] = 0; continue; }
+        const int e = ilogb(mx);
+        double part[256];
+        for (int t = 0; t < 256; t++) {
+            double ss = 0;
+            for (int k = t; k < len; k += 256) { const double v = ldexp(X[r * sRow + k * sCol], -e); ss = fma(v, v, ss); }
+            part[t] = ss;
+        }
+        double w[8];
+        for (int wp = 0; wp < 8; wp++) {
+            double v[32], u[32];
+            for (int l = 0; l < 32; l++) v[l] = part[32 * wp + l];
+            for (int o = 16; o; o >>= 1) {
+                for (int l = 0; l < 32; l++) u[l] = v[l ^ o];
+                for (int l = 0; l < 32; l++) v[l] = v[l] + u[l];
+            }
+            w[wp] = v[0];
+        }
+        double ss = w[0];
+        for (int i = 1; i < 8; i++) ss = ss + w[i];
+        s[r] = beta - 1 - (e + ilogb(sqrt(ss) * (1 + 0x1p-30)));
+    }
+}
+
+/* bench/oz_strassen.cu:247 -- the bits of the 2-norm mode: floor((log2 P - 1.001) / 2), at most 62 */
+int oz_oracle_bits_for_norm(int nm) {
+    double l2 = 0;
+    for (int l = 0; l < nm; l++) l2 += log2((double)MODULI[l]);
+    const int b = (int)floor((l2 - 1.001) / 2);
+    return b > 62 ? 62 : b;
+}
+
+/* the product with the 2-norm scales in place of the max-based ones (everything else as oz_oracle_dgemm) */
+int oz_oracle_dgemm_norm(int M, int N, int K, const double *A, const double *B, double *C, int nm) {
+    if (M <= 0 || N <= 0 || K <= 0 || nm < 1 || nm > OZ_MAXM || K >= 131072) return -2;
+    const int bits = oz_oracle_bits_for_norm(nm);
+    const size_t pa = (size_t)M * K, pb = (size_t)N * K, pc = (size_t)M * N;
+    int8_t *Ar = calloc((size_t)nm * pa, 1), *Br = calloc((size_t)nm * pb, 1);
+    int32_t *Cl = malloc((size_t)nm * pc * 4);
+    int *sa = malloc((size_t)M * 4), *sb = malloc((size_t)N * 4);
+    int rc = 0;
+    if (!Ar || !Br || !Cl || !sa || !sb) rc = -3;
+    else {
+        oz_oracle_scales_norm(A, M, K, K, 1, bits, sa);
+        oz_oracle_scales_norm(B, N, K, 1, N, bits, sb);
+        oz_oracle_residues(A, M, K, K, 1, sa, nm, Ar, K, pa);
+        oz_oracle_residues(B, N, K, 1, N, sb, nm, Br, K, pb);
+        for (int l = 0; l < nm; l++) oz_oracle_gemm_i8(Ar + l * pa, Br + l * pb, Cl + l * pc, M, N, K, K, K, N);
+        oz_oracle_crt(Cl, pc, M, N, N, sa, sb, nm, C, N);
+    }
+    free(Ar); free(Br); free(Cl); free(sa); free(sb);
+    return rc;
+}

@@ -587,6 +587,26 @@ OZB_API int ozb_dgemm_ex(int M, int N, int K, const double *A, long long lda, co
     return plan_dgemm(p, A, lda, B, ldb, C, ldc, (cudaStream_t)stream);
 }
 
+// bench/oz_strassen.cu:74-97,247 -- the product with the reference's optional 2-norm scales: beta = floor((log2 P - 1.001) / 2)
+OZB_API int ozb_dgemm_norm(int M, int N, int K, const double *A, long long lda, const double *B, long long ldb, double *C, long long ldc,
+                           int moduli, void *stream) {
+    if (int e = check_args(M, N, K)) return e;
+    if (moduli < 8 || moduli > 16 || !A || !B || !C || lda < K || ldb < N || ldc < N) return OZB_EARG;
+    std::lock_guard<std::mutex> g(mu);
+    ozb_plan *p;
+    if (int e = plan_for(0, M, N, K, moduli, 62, &p)) return e;
+    double l2 = 0;
+    for (int l = 0; l < moduli; l++) l2 += log2((double)modulus(l));
+    int beta = (int)floor((l2 - 1.001) / 2);
+    if (beta > 62) beta = 62;
+    cudaStream_t st = (cudaStream_t)stream;
+    p->last = st;
+    cudaError_t e = norm_scale_residues_rows(p->nm, A, M, K, lda, beta, p->sa, p->Ar, p->Kp, p->planeA, st);
+    if (!e) e = norm_scale_residues_cols(p->nm, B, K, N, ldb, beta, p->sb, p->Br, p->Kp, p->planeB, st);
+    if (!e) e = gemm_chunks(p, p->Br, p->Cr, N, st);
+    if (!e) e = crt_from_i8(p->nm, p->Cr, p->planeC, M, N, p->Np, p->sa, p->sb, C, ldc, st);
+    return (int)e;
+}
 OZB_API int ozb_scale_residues_rows(int moduli, const double *X, int rows, int len, long long ldx, int bits, int *s, int8_t *R,
                                     int ld, size_t plane, void *stream) {
     if (int e = check_args(rows, 1, len)) return e;

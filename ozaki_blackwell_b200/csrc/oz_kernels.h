@@ -13,6 +13,10 @@ cudaError_t scale_residues_cols(int nm, const double *X, int rows, int cols, lon
 cudaError_t cols_absmax_accumulate(const double *X, int rows, int cols, long long ldx, unsigned long long *colmax, cudaStream_t st);
 cudaError_t cols_residues_from_max(int nm, const double *X, int rows, int cols, long long ldx, int bits, const unsigned long long *colmax,
                                    int *s, int8_t *R, int ld, size_t plane, cudaStream_t st);
+cudaError_t norm_scale_residues_rows(int nm, const double *X, int rows, int len, long long ldx, int beta, int *s, int8_t *R, int ld,
+                                     size_t plane, cudaStream_t st);
+cudaError_t norm_scale_residues_cols(int nm, const double *X, int rows, int cols, long long ldx, int beta, int *s, int8_t *R, int ld,
+                                     size_t plane, cudaStream_t st);
 cudaError_t gemm_i8_planes(const int8_t *A, const int8_t *Bt, void *C, int M, int N, int K, int Z, long long lda, long long ldb,
                            long long ldc, size_t pa, size_t pb, size_t pc, int fused, int first_modulus, int *status, int sms,
                            cudaStream_t st, int accumulate = 0);

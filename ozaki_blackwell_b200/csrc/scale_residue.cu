@@ -49,7 +49,7 @@ __device__ __forceinline__ void residues_of_4(const long long (&v)[4], Put &&put
 // ---------------------------------------------------------------------------------------------------------------
 // A side: one block per row. R chunks of four doubles per thread stay in registers between the two phases.
 // ---------------------------------------------------------------------------------------------------------------
-template <int NM, int R, int MAXT>
+template <int NM, int R, int MAXT, bool GIVEN = false>   // GIVEN: the scales are already in s_out (2-norm mode), no max pass
 __global__ void __launch_bounds__(MAXT) row_scale_residues(const double *__restrict__ X, int len, long long ldx, int bits,
                                                            int *__restrict__ s_out, int8_t *__restrict__ Rp, int ld,
                                                            size_t plane) {
@@ -79,7 +79,7 @@ __global__ void __launch_bounds__(MAXT) row_scale_residues(const double *__restr
 #pragma unroll
             for (int e = 0; e < 4; e++) mx = fmax(mx, fabs(x[i][e]));
         }
-    } else {
+    } else if (!GIVEN) {
         for (int c = tid; c < chunks; c += nt) {
             double d[4];
             load4(c, d);
@@ -87,16 +87,21 @@ __global__ void __launch_bounds__(MAXT) row_scale_residues(const double *__restr
             for (int e = 0; e < 4; e++) mx = fmax(mx, fabs(d[e]));
         }
     }
-    // block max: shuffles inside the warp, shared memory across warps
-    __shared__ double wmax[32];
+    int s;
+    if constexpr (GIVEN) {
+        s = s_out[r];
+    } else {
+        // block max: shuffles inside the warp, shared memory across warps
+        __shared__ double wmax[32];
 #pragma unroll
-    for (int o = 16; o; o >>= 1) mx = fmax(mx, __shfl_xor_sync(~0u, mx, o));
-    if ((tid & 31) == 0) wmax[tid >> 5] = mx;
-    __syncthreads();
-    mx = wmax[0];
-    for (int w = 1; w < (nt >> 5); w++) mx = fmax(mx, wmax[w]);
-    const int s = scale_from_max(mx, bits);
-    if (tid == 0) s_out[r] = s;
+        for (int o = 16; o; o >>= 1) mx = fmax(mx, __shfl_xor_sync(~0u, mx, o));
+        if ((tid & 31) == 0) wmax[tid >> 5] = mx;
+        __syncthreads();
+        mx = wmax[0];
+        for (int w = 1; w < (nt >> 5); w++) mx = fmax(mx, wmax[w]);
+        s = scale_from_max(mx, bits);
+        if (tid == 0) s_out[r] = s;
+    }
 
     const bool fast = s >= -1022 && s <= 1023;
     const double p2 = pow2_normal(fast ? s : 0);
@@ -174,8 +179,9 @@ __global__ void __launch_bounds__(256) col_residues_t(const double *__restrict__
     {
         const int j = j0 + lane, k0 = kb + warp * 16;
         if (j < cols && k0 < rows) {
-            const int s = scale_from_max(__longlong_as_double((long long)colmax[j]), bits);
-            if (blockIdx.y == 0 && warp == 0) s_out[j] = s;
+            // colmax == nullptr: the scales are already in s_out (2-norm mode)
+            const int s = colmax ? scale_from_max(__longlong_as_double((long long)colmax[j]), bits) : s_out[j];
+            if (colmax && blockIdx.y == 0 && warp == 0) s_out[j] = s;
             const bool fast = s >= -1022 && s <= 1023;
             const double p2 = pow2_normal(fast ? s : 0);
             double d[16];
@@ -205,6 +211,61 @@ __global__ void __launch_bounds__(256) col_residues_t(const double *__restrict__
             const uint4 v = *reinterpret_cast<const uint4 *>(tile + (l * CT_COLS + j) * CT_PITCH + c * 16);
             *reinterpret_cast<uint4 *>(Rp + (size_t)l * plane + (size_t)(j0 + j) * ld + kpos) = v;
         }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Optional scale from the 2-norm (the reference's scales_norm, bench/oz_strassen.cu:74-97): s = beta - 1 - (e + ilogb(
+// sqrt(ss) (1 + 2^-30))), e = ilogb(max |x|), ss = sum (x 2^-e)^2. The last bits of ss can move s across a power of two,
+// so the sum is taken in the reference's order: 256 threads, thread t accumulates k = t, t + 256, ... with fma, a
+// butterfly of additions inside each warp, then the eight warp sums in order. `vecs` vectors per block (1 for rows, 4
+// adjacent columns for a row-major matrix so that each thread reads whole 32-byte sectors).
+// ---------------------------------------------------------------------------------------------------------------
+template <int VECS>
+__global__ void __launch_bounds__(256) scales_norm_kernel(const double *__restrict__ X, int nvec, int len, long long sVec, long long sElem,
+                                                          int beta, int *__restrict__ s) {
+    const int v0 = blockIdx.x * VECS, tid = threadIdx.x;
+    __shared__ double w[VECS][8];
+    __shared__ int se[VECS];
+    __shared__ bool zero[VECS];
+    double acc[VECS];
+#pragma unroll
+    for (int q = 0; q < VECS; q++) acc[q] = 0;
+    for (int k = tid; k < len; k += 256)
+#pragma unroll
+        for (int q = 0; q < VECS; q++)
+            if (v0 + q < nvec) acc[q] = fmax(acc[q], fabs(X[(size_t)(v0 + q) * sVec + (size_t)k * sElem]));
+#pragma unroll
+    for (int q = 0; q < VECS; q++) {
+        for (int o = 16; o; o >>= 1) acc[q] = fmax(acc[q], __shfl_xor_sync(~0u, acc[q], o));
+        if ((tid & 31) == 0) w[q][tid >> 5] = acc[q];
+    }
+    __syncthreads();
+    if (tid < VECS) {
+        double m = w[tid][0];
+        for (int i = 1; i < 8; i++) m = fmax(m, w[tid][i]);
+        zero[tid] = m == 0;
+        se[tid] = m == 0 ? 0 : ilogb(m);
+    }
+    __syncthreads();
+    int e[VECS];
+#pragma unroll
+    for (int q = 0; q < VECS; q++) { e[q] = se[q]; acc[q] = 0; }
+    for (int k = tid; k < len; k += 256)
+#pragma unroll
+        for (int q = 0; q < VECS; q++)
+            if (v0 + q < nvec) { const double v = ldexp(X[(size_t)(v0 + q) * sVec + (size_t)k * sElem], -e[q]); acc[q] = fma(v, v, acc[q]); }
+    __syncthreads();   // w is reused
+#pragma unroll
+    for (int q = 0; q < VECS; q++) {
+        for (int o = 16; o; o >>= 1) acc[q] = acc[q] + __shfl_xor_sync(~0u, acc[q], o);
+        if ((tid & 31) == 0) w[q][tid >> 5] = acc[q];
+    }
+    __syncthreads();
+    if (tid < VECS && v0 + tid < nvec) {
+        double t = w[tid][0];
+        for (int i = 1; i < 8; i++) t = t + w[tid][i];
+        s[v0 + tid] = zero[tid] ? 0 : beta - 1 - (se[tid] + ilogb(sqrt(t) * (1 + 0x1p-30)));
     }
 }
 
@@ -245,6 +306,32 @@ static cudaError_t launch_cols_t(const double *X, int rows, int cols, long long 
     default: return cudaErrorInvalidValue;                                                                        \
     }
 
+cudaError_t cols_residues_from_max(int nm, const double *X, int rows, int cols, long long ldx, int bits, const unsigned long long *colmax,
+                                   int *s, int8_t *R, int ld, size_t plane, cudaStream_t st);
+template <int NM>
+static cudaError_t launch_rows_given_t(const double *X, int rows, int len, long long ldx, int *s, int8_t *R, int ld, size_t plane,
+                                       cudaStream_t st) {
+    constexpr int RR = 8, MAXT = 512;
+    int nt = ((len + 3) / 4 + RR - 1) / RR;
+    nt = (nt + 31) / 32 * 32;
+    if (nt < 32) nt = 32;
+    if (nt > MAXT) nt = MAXT;
+    row_scale_residues<NM, RR, MAXT, true><<<rows, nt, 0, st>>>(X, len, ldx, 0, s, R, ld, plane);
+    return cudaGetLastError();
+}
+// The 2-norm mode of both operands: scales first (reference order of summation), then the residue passes with those scales
+cudaError_t norm_scale_residues_rows(int nm, const double *X, int rows, int len, long long ldx, int beta, int *s, int8_t *R, int ld,
+                                     size_t plane, cudaStream_t st) {
+    scales_norm_kernel<1><<<rows, 256, 0, st>>>(X, rows, len, ldx, 1, beta, s);
+    if (cudaError_t e = cudaGetLastError()) return e;
+    OZ_DISPATCH_NM(nm, (launch_rows_given_t<NM>(X, rows, len, ldx, s, R, ld, plane, st)));
+}
+cudaError_t norm_scale_residues_cols(int nm, const double *X, int rows, int cols, long long ldx, int beta, int *s, int8_t *R, int ld,
+                                     size_t plane, cudaStream_t st) {
+    scales_norm_kernel<4><<<(cols + 3) / 4, 256, 0, st>>>(X, cols, rows, 1, ldx, beta, s);
+    if (cudaError_t e = cudaGetLastError()) return e;
+    return cols_residues_from_max(nm, X, rows, cols, ldx, 0, nullptr, s, R, ld, plane, st);
+}
 // A-like operand: `rows` rows of `len` contiguous doubles, row pitch ldx; writes s[rows] and R[nm][rows][ld]
 cudaError_t scale_residues_rows(int nm, const double *X, int rows, int len, long long ldx, int bits, int *s, int8_t *R, int ld,
                                 size_t plane, cudaStream_t st) {

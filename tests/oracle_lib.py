@@ -227,3 +227,32 @@ def ref_fill_dd(M, N, K, spread):
     Bh, Bl = np.empty(K * N), np.empty(K * N)
     lib.oz_ref_fill_dd(_ptr(Ah), _ptr(Al), M * K, _ptr(Bh), _ptr(Bl), K * N, float(spread), K + int(spread))
     return Ah.reshape(M, K), Al.reshape(M, K), Bh.reshape(K, N), Bl.reshape(K, N)
+
+
+# ---- optional 2-norm scaling (bench/oz_strassen.cu:74-97 of the reference) ----
+lib.oz_oracle_scales_norm.argtypes = [_p, _i, _i, _ll, _ll, _i, _p]
+lib.oz_oracle_scales_norm.restype = None
+lib.oz_oracle_bits_for_norm.argtypes = [_i]
+lib.oz_oracle_dgemm_norm.argtypes = [_i, _i, _i, _p, _p, _p, _i]
+
+
+def scales_norm(X, rows, length, s_row, s_col, beta):
+    X = _c(X)
+    s = np.empty(rows, dtype=np.int32)
+    lib.oz_oracle_scales_norm(_ptr(X), rows, length, s_row, s_col, beta, _ptr(s))
+    return s
+
+
+def bits_for_norm(nm):
+    return lib.oz_oracle_bits_for_norm(nm)
+
+
+def dgemm_norm(A, B, nm=16):
+    A, B = _c(A), _c(B)
+    M, K = A.shape
+    N = B.shape[1]
+    C = np.empty((M, N))
+    rc = lib.oz_oracle_dgemm_norm(M, N, K, _ptr(A), _ptr(B), _ptr(C), nm)
+    if rc:
+        raise RuntimeError(f"oracle dgemm_norm failed: {rc}")
+    return C
