@@ -246,7 +246,11 @@ def run_ours(args):
                 best = max(best, tops_p.value)
             probe["cta_pair" if pair else "one_cta"] = best
         peak = max(probe.values())
-        roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+        # DRAM bytes of one GEMM launch: the ncu capture at n = 4096 (profiles/gemm_i8_tc2_n4096_16moduli.md) measured
+        # 785.7 MB against 805.3 MB of algorithmic bytes (every residue byte read once, every product byte written once);
+        # traffic is proportional to those bytes, so it is scaled to this launch by them
+        traffic = 785.7 / 805.3 * nm * (M * K + N * K + M * N)
+        roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": traffic,
                 "kernel": "gemm_i8_tc2<fused mod> (cta_group::2)", "peak_probe_int8_tops": probe,
                 "note": "INT8 tera-operations/s. peak = tensor-pipe probe measured in this run on this GPU (MEASURED_PEAKS.json holds "
                 f"no INT8 figure); for comparison 2 x measured dense bf16: sustained {2 * pk['bf16']:.0f}, burst {2 * pk['bf16_burst']:.0f} "
