@@ -25,7 +25,7 @@ using namespace ozk;
 // ---------------------------------------------------------------------------------------------------------------
 constexpr int HOST_PANELS = 32;
 struct ozb_plan {
-    int M, N, K, nm, bits, maxbits;
+    int M, N, K, nm, bits, maxbits, dev;   // dev: the device the workspaces live on
     int Kp, Np;                      // pitch of the residue planes of A and B (bytes); pitch of the product planes (bytes)
     size_t planeA, planeB, planeC;   // plane pitches in bytes
     int8_t *Ar, *Br, *Cr;
@@ -105,6 +105,7 @@ static int plan_make(int M, int N, int K, int nm, int maxbits, ozb_plan **out) {
     ozb_plan *p = new ozb_plan();
     memset(p, 0, sizeof *p);
     p->M = M; p->N = N; p->K = K; p->nm = nm; p->maxbits = maxbits;
+    cudaGetDevice(&p->dev);
     p->bits = bits_for_impl(nm, K, maxbits);
     p->Kp = round_up(K, 128);   // rows start on 128-byte lines; the TMA extent is K itself, so the padding is never read
     { const char *env = getenv("OZ_KPAD"); if (env && *env) p->Kp += atoi(env) / 128 * 128; }   // experiment: break power-of-two pitches
@@ -332,7 +333,9 @@ int check_args(int M, int N, int K) {   // python/capi.cu:23-29
 }
 int plan_for(int which, int M, int N, int K, int nm, int maxbits, ozb_plan **out) {   // python/capi.cu:30-35
     Cache &c = cache[which];
-    if (c.p && (c.p->M != M || c.p->N != N || c.p->K != K || c.p->nm != nm || c.p->maxbits != maxbits)) { plan_free(c.p); c.p = nullptr; }
+    int dev = -1;
+    cudaGetDevice(&dev);   // a cached plan is only good on the device it was made on
+    if (c.p && (c.p->M != M || c.p->N != N || c.p->K != K || c.p->nm != nm || c.p->maxbits != maxbits || c.p->dev != dev)) { plan_free(c.p); c.p = nullptr; }
     if (!c.p) if (int e = plan_make(M, N, K, nm, maxbits, &c.p)) { c.p = nullptr; return e; }
     *out = c.p;
     return 0;

@@ -302,8 +302,8 @@ static cudaError_t rows_dd_t(const double *Xh, const double *Xl, int rows, int l
 template <int NM>
 static cudaError_t cols_dd_t(const double *Xh, const double *Xl, int rows, int cols, long long ldx, int bits, unsigned long long *colmax,
                              int *s, int8_t *R, int ld, size_t plane, cudaStream_t st) {
-    static const cudaError_t attr = cudaFuncSetAttribute(col_residues_t_dd<NM>, cudaFuncAttributeMaxDynamicSharedMemorySize, dd_tile_smem<NM>());
-    if (attr) return attr;
+    static PerDevice pd;
+    if (cudaError_t a = pd.once([] { return cudaFuncSetAttribute(col_residues_t_dd<NM>, cudaFuncAttributeMaxDynamicSharedMemorySize, dd_tile_smem<NM>()); })) return a;
     cudaError_t e = cudaMemsetAsync(colmax, 0, (size_t)cols * 8, st);
     if (e) return e;
     col_absmax_dd<<<dim3((cols + 255) / 256, (rows + 63) / 64), 256, 0, st>>>(Xh, rows, cols, ldx, colmax);

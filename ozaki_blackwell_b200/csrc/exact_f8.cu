@@ -314,7 +314,7 @@ __global__ void __launch_bounds__(128) crt_round(const int8_t *__restrict__ Cr, 
 
 // workspace kept between calls of the same shape
 struct Work {
-    int M = 0, N = 0, K = 0, nm = 0, Kp = 0, Np = 0;
+    int M = 0, N = 0, K = 0, nm = 0, Kp = 0, Np = 0, dev = -1;
     int8_t *Xr = nullptr, *Wr = nullptr, *Cr = nullptr;
     RowInfo *rinfo = nullptr;
     ColInfo *cinfo = nullptr;
@@ -377,9 +377,11 @@ int exact_bf16_fp8_gemm(int M, int N, int K, const uint16_t *X, long long ldx, c
     // workspace
     Work &wk = work;
     const int Kp = (K + 127) / 128 * 128, Np = (N + 15) / 16 * 16;
-    if (wk.M != M || wk.N != N || wk.K != K) {
+    int dev = -1;
+    cudaGetDevice(&dev);
+    if (wk.M != M || wk.N != N || wk.K != K || wk.dev != dev) {
         wk.release();
-        wk.M = M; wk.N = N; wk.K = K; wk.Kp = Kp; wk.Np = Np;
+        wk.M = M; wk.N = N; wk.K = K; wk.Kp = Kp; wk.Np = Np; wk.dev = dev;
         e = cudaMalloc(&wk.rinfo, (size_t)M * sizeof(RowInfo));
         if (!e) e = cudaMalloc(&wk.cinfo, (size_t)nbj * sizeof(ColInfo));
         if (!e) e = cudaMalloc(&wk.mult, (size_t)nbk * nbj * 8);
@@ -416,8 +418,8 @@ int exact_bf16_fp8_gemm(int M, int N, int K, const uint16_t *X, long long ldx, c
         if (e) { wk.release(); return (int)e; }
         wk.nm = nm;
     }
-    static const cudaError_t attr = cudaFuncSetAttribute(w_residues_t, cudaFuncAttributeMaxDynamicSharedMemorySize, WT_SMEM);
-    if (attr) return (int)attr;
+    static PerDevice pd;
+    if (cudaError_t a = pd.once([] { return cudaFuncSetAttribute(w_residues_t, cudaFuncAttributeMaxDynamicSharedMemorySize, WT_SMEM); })) return (int)a;
     // 3. residues, GEMMs; 4. reconstruction and rounding
     x_residues<<<M, 256, 0, st>>>(X, K, ldx, wk.rinfo, nm, wk.Xr, Kp, (size_t)M * Kp);
     w_residues_t<<<dim3((N + WT_COLS - 1) / WT_COLS, nbk), 256, WT_SMEM, st>>>(W, K, N, ldw, wk.mult, nbj, nm, wk.Wr, Kp, (size_t)N * Kp);

@@ -118,7 +118,13 @@ struct Params {
     int *status;                  // device word: set to 1 when a wait timed out
 };
 
-__constant__ ModConsts c_modc[MAXM];
+struct ModTable { ModConsts v[MAXM]; };
+constexpr ModTable make_mod_table() {
+    ModTable t{};
+    for (int l = 0; l < MAXM; l++) t.v[l] = mod_consts(l);
+    return t;
+}
+__constant__ ModTable c_modt = make_mod_table();   // part of the device image: present on every device that loads the library
 constexpr bool epilogue_reduction_exact() {
     for (int l = 0; l < MAXM; l++)
         if (!magic_ok(l, epi_umax(l))) return false;
@@ -258,7 +264,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_i8_tc(const __grid_constant__
             int z, tm, tn;
             decode_work(p, w, z, tm, tn);
             const uint32_t acc = n & 1u;
-            if constexpr (FUSED_MOD) mc = c_modc[p.first_modulus + z];
+            if constexpr (FUSED_MOD) mc = c_modt.v[p.first_modulus + z];
             // every lane waits (each needs the barrier's acquire); the vote keeps the warp together if one gave up
             if (!__all_sync(~0u, mbar_wait(accfull_bar(acc), (n >> 1) & 1u, abortp))) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -455,7 +461,7 @@ gemm_i8_tc2(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
             int z, tm, tn;
             decode_work(pp, w, z, tm, tn);
             const uint32_t acc = n & 1u;
-            if constexpr (FUSED_MOD) mc = c_modc[p.first_modulus + z];
+            if constexpr (FUSED_MOD) mc = c_modt.v[p.first_modulus + z];
             if (!__all_sync(~0u, mbar_wait(accfull_bar(acc), (n >> 1) & 1u, abortp, 0x40 + (int)rank + ((int)(n & 0xfff) << 8)))) break;
             if (rank == 0 && warp == 2 && lane == 0) mbar_arrive_cluster(map_to_cta(accfull_bar(acc), 1));   // tell the peer's epilogue
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -599,21 +605,17 @@ static cudaError_t make_map(CUtensorMap *map, const int8_t *ptr, int K, int rows
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
-static cudaError_t gemm_setup() {
-    static cudaError_t once = [] {
-        ModConsts h[MAXM];
-        for (int l = 0; l < MAXM; l++) h[l] = mod_consts(l);
-        cudaError_t e = cudaMemcpyToSymbol(g8::c_modc, h, sizeof h);
-        if (e) return e;
-        e = cudaFuncSetAttribute(g8::gemm_i8_tc<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, g8::SMEM_BYTES);
-        if (e) return e;
-        e = cudaFuncSetAttribute(g8::gemm_i8_tc<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, g8::SMEM_BYTES);
-        if (e) return e;
-        e = cudaFuncSetAttribute(g8::gemm_i8_tc2<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, g8::two::SMEM2_BYTES);
-        if (e) return e;
-        return cudaFuncSetAttribute(g8::gemm_i8_tc2<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, g8::two::SMEM2_BYTES);
-    }();
-    return once;
+static cudaError_t gemm_setup() {   // the kernels' shared-memory opt-in, on every device the process uses
+    static PerDevice pd;
+    return pd.once([] {
+        cudaError_t e = cudaFuncSetAttribute(g8::gemm_i8_tc<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, g8::SMEM_BYTES);
+        if (!e) e = cudaFuncSetAttribute(g8::gemm_i8_tc<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, g8::SMEM_BYTES);
+        if (!e) e = cudaFuncSetAttribute(g8::gemm_i8_tc2<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, g8::two::SMEM2_BYTES);
+        if (!e) e = cudaFuncSetAttribute(g8::gemm_i8_tc2<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, g8::two::SMEM2_BYTES);
+        if (!e) e = cudaFuncSetAttribute(g8::tensor_peak_probe<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, g8::SMEM_BYTES);
+        if (!e) e = cudaFuncSetAttribute(g8::tensor_peak_probe<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, g8::SMEM_BYTES);
+        return e;
+    });
 }
 
 // C[z] = A[z] * Bt[z]^T for z < Z. A: [Z][M][lda] int8, Bt: [Z][N][ldb] int8 (pitches in bytes, multiples of 16; plane
@@ -652,8 +654,11 @@ cudaError_t gemm_i8_planes(const int8_t *A, const int8_t *Bt, void *C, int M, in
     if (total > 0x7fffffffLL) return cudaErrorInvalidValue;
     if (pair) {
         // A persistent grid must be fully resident: ask how many 2-CTA clusters of this kernel the device can hold at once
-        static int max_pairs[2] = {0, 0};
-        if (!max_pairs[fused ? 1 : 0]) {
+        static int max_pairs[64][2] = {};   // per device
+        int dev_ = 0;
+        cudaGetDevice(&dev_);
+        int (&mp)[2] = max_pairs[dev_ & 63];
+        if (!mp[fused ? 1 : 0]) {
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3(sms & ~1); cfg.blockDim = dim3(g8::THREADS); cfg.dynamicSmemBytes = g8::two::SMEM2_BYTES;
             cudaLaunchAttribute at[1];
@@ -664,11 +669,11 @@ cudaError_t gemm_i8_planes(const int8_t *A, const int8_t *Bt, void *C, int M, in
                                   : cudaOccupancyMaxActiveClusters(&n, g8::gemm_i8_tc2<false>, &cfg);
             if (q != cudaSuccess || n <= 0) { cudaGetLastError(); n = sms / 2; }
             if (n > sms / 2) n = sms / 2;
-            max_pairs[fused ? 1 : 0] = n;
+            mp[fused ? 1 : 0] = n;
             if (getenv("OZ_DEBUG")) fprintf(stderr, "ozb: %d SMs, at most %d resident CTA pairs\n", sms, n);
         }
         const long long pairs_total = (long long)((M + g8::two::BM2 - 1) / g8::two::BM2) * p.tiles_n * Z;
-        const int limit = max_pairs[fused ? 1 : 0];
+        const int limit = mp[fused ? 1 : 0];
         const int pairs = (int)(pairs_total < limit ? pairs_total : limit);
         if (fused) g8::gemm_i8_tc2<true><<<2 * pairs, g8::THREADS, g8::two::SMEM2_BYTES, st>>>(mapA, mapB, p);
         else g8::gemm_i8_tc2<false><<<2 * pairs, g8::THREADS, g8::two::SMEM2_BYTES, st>>>(mapA, mapB, p);
@@ -687,11 +692,6 @@ cudaError_t int8_peak_probe(int iters, int pair, float *ms, double *tops, int *s
     if (iters <= 0 || iters > (1 << 22)) return cudaErrorInvalidValue;
     cudaError_t e = gemm_setup();
     if (e) return e;
-    static const cudaError_t attr = [] {
-        cudaError_t a = cudaFuncSetAttribute(g8::tensor_peak_probe<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, g8::SMEM_BYTES);
-        return a ? a : cudaFuncSetAttribute(g8::tensor_peak_probe<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, g8::SMEM_BYTES);
-    }();
-    if (attr) return attr;
     int dev, sms;
     if ((e = cudaGetDevice(&dev))) return e;
     if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev))) return e;

@@ -6,6 +6,21 @@
 
 namespace ozk {
 
+// A kernel attribute (or anything else that belongs to a device's context) has to be set once on EVERY device a process
+// uses, not once per process: run `f` the first time the calling site is reached with each device current.
+struct PerDevice {
+    unsigned long long seen = 0;   // one bit per device ordinal (0..63)
+    template <class F> cudaError_t once(F &&f) {
+        int dev = 0;
+        if (cudaError_t e = cudaGetDevice(&dev)) return e;
+        if (dev < 0 || dev > 63) return cudaErrorInvalidDevice;
+        if (seen >> dev & 1ull) return cudaSuccess;
+        if (cudaError_t e = f()) return e;
+        seen |= 1ull << dev;       // callers hold the library's mutex or tolerate a repeated, idempotent call
+        return cudaSuccess;
+    }
+};
+
 __device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c) {   // signed bytes x signed bytes
     int d;
     asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));

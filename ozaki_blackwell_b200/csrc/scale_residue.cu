@@ -289,8 +289,8 @@ static cudaError_t launch_cols_t(const double *X, int rows, int cols, long long 
     cudaError_t e = cudaMemsetAsync(colmax, 0, (size_t)cols * 8, st);
     if (e) return e;
     col_absmax<<<dim3((cols + 511) / 512, (rows + CM_ROWS - 1) / CM_ROWS), 256, 0, st>>>(X, rows, cols, ldx, colmax);
-    static const cudaError_t attr = cudaFuncSetAttribute(col_residues_t<NM>, cudaFuncAttributeMaxDynamicSharedMemorySize, col_tile_smem<NM>());
-    if (attr) return attr;
+    static PerDevice pd;
+    if (cudaError_t a = pd.once([] { return cudaFuncSetAttribute(col_residues_t<NM>, cudaFuncAttributeMaxDynamicSharedMemorySize, col_tile_smem<NM>()); })) return a;
     col_residues_t<NM><<<dim3((cols + CT_COLS - 1) / CT_COLS, (rows + CT_K - 1) / CT_K), 256, col_tile_smem<NM>(), st>>>(
         X, rows, cols, ldx, colmax, bits, s, R, ld, plane);
     return cudaGetLastError();
@@ -347,8 +347,8 @@ cudaError_t cols_absmax_accumulate(const double *X, int rows, int cols, long lon
 template <int NM>
 static cudaError_t launch_cols_residues_t(const double *X, int rows, int cols, long long ldx, int bits, const unsigned long long *colmax,
                                           int *s, int8_t *R, int ld, size_t plane, cudaStream_t st) {
-    static const cudaError_t attr = cudaFuncSetAttribute(col_residues_t<NM>, cudaFuncAttributeMaxDynamicSharedMemorySize, col_tile_smem<NM>());
-    if (attr) return attr;
+    static PerDevice pd;
+    if (cudaError_t a = pd.once([] { return cudaFuncSetAttribute(col_residues_t<NM>, cudaFuncAttributeMaxDynamicSharedMemorySize, col_tile_smem<NM>()); })) return a;
     col_residues_t<NM><<<dim3((cols + CT_COLS - 1) / CT_COLS, (rows + CT_K - 1) / CT_K), 256, col_tile_smem<NM>(), st>>>(
         X, rows, cols, ldx, colmax, bits, s, R, ld, plane);
     return cudaGetLastError();

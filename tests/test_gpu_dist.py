@@ -49,3 +49,21 @@ def test_two_gpus_bit_identical_to_one(tmp_path, src):
     want = g.gpu_dgemm(A, B, nm)
     got = np.vstack([np.load(tmp_path / f"c{r}.npy") for r in range(2)])
     assert g.same_bits(got, want), g.describe_mismatch(got, want)
+
+
+def test_one_process_two_devices():
+    """A process that switches devices: per-device kernel attributes, constant tables and plan caches must follow."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import gpu_util as g
+    import oracle_lib as o
+    A, B = g.synthetic(300, 260, 71), g.synthetic(260, 280, 72)
+    want = o.dgemm(A, B, 16)
+    try:
+        for dev in (0, 1, 0, 1):
+            torch.cuda.set_device(dev)
+            got = g.gpu_dgemm(A, B, 16)
+            assert g.same_bits(got, want), (dev, g.describe_mismatch(got, want))
+    finally:
+        torch.cuda.set_device(0)
