@@ -170,6 +170,10 @@ int ozb_crt_i8(int moduli, const int8_t *Cr, size_t plane, int M, int N, long lo
  * pseudo-random bytes, `iters` (1..2^22) rounds of 8 instructions per CTA (pair = 0) or per CTA pair (pair = 1,
  * cta_group::2). Synchronous. Returns the elapsed ms and tera-operations per second (2 ops per multiply-add). */
 int ozb_int8_peak(int iters, int pair, float *ms, double *tops);
+/* No counterpart in the reference (its kernels have no waits that could expire). Self-test of the failure path: one CTA
+ * waits, with a budget of budget_ms (1..2000), on a barrier that nothing completes. The expected return value is
+ * OZB_ETIMEOUT: the wait gave up, raised the status word and the kernel returned normally; the context stays usable. */
+int ozb_selftest_wait_expiry(int budget_ms);
 /* Status of the stage calls above (they share one device status word per device): 0 or OZB_ETIMEOUT. Synchronises
  * the device. */
 int ozb_status(void);

@@ -55,6 +55,7 @@ lib.ozb_gemm_i8_mod.argtypes = [_p, _p, _p, _i, _i, _i, _i, _ll, _ll, _ll, _sz, 
 lib.ozb_crt_i32.argtypes = [_i, _p, _sz, _i, _i, _ll, _p, _p, _p, _ll, _p]
 lib.ozb_crt_i8.argtypes = [_i, _p, _sz, _i, _i, _ll, _p, _p, _p, _ll, _p]
 lib.ozb_int8_peak.argtypes = [_i, _i, ctypes.POINTER(ctypes.c_float), ctypes.POINTER(ctypes.c_double)]
+lib.ozb_selftest_wait_expiry.argtypes = [_i]
 lib.ozb_status.argtypes = []
 
 # every symbol include/ozb.h declares; tests check that the library exports each one
@@ -63,5 +64,5 @@ SYMBOLS = [
     "ozb_bits_for", "ozb_modulus", "ozb_plan_create", "ozb_plan_destroy", "ozb_plan_dgemm", "ozb_plan_set_a",
     "ozb_plan_panel", "ozb_plan_view", "ozb_plan_status", "ozb_plan_profile", "ozb_plan_phase_ms", "ozb_dgemm_ex", "ozb_dgemm_norm", "ozb_ddgemm_ex", "ozb_bf16_fp8_gemm",
     "ozb_scale_residues_rows", "ozb_scale_residues_cols", "ozb_scale_residues_cols_static", "ozb_gemm_i8", "ozb_gemm_i8_mod", "ozb_crt_i32", "ozb_crt_i8",
-    "ozb_status", "ozb_int8_peak",
+    "ozb_status", "ozb_int8_peak", "ozb_selftest_wait_expiry",
 ]

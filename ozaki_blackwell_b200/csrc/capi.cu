@@ -670,6 +670,14 @@ OZB_API int ozb_int8_peak(int iters, int pair, float *ms, double *tops) {
     if (int e = (int)int8_peak_probe(iters, pair, ms, tops, st, 0)) return e == (int)cudaErrorInvalidValue ? OZB_EARG : e;
     return read_status(st);
 }
+OZB_API int ozb_selftest_wait_expiry(int budget_ms) {
+    if (int e = check_args(1, 1, 1)) return e;
+    int *st = status_word();
+    if (!st) return (int)cudaErrorMemoryAllocation;
+    if (int e = (int)wait_expiry_selftest((unsigned)budget_ms, st, 0)) return e == (int)cudaErrorInvalidValue ? OZB_EARG : e;
+    if (int e = (int)cudaDeviceSynchronize()) return e;
+    return read_status(st);
+}
 OZB_API int ozb_status(void) {
     if (int e = (int)cudaDeviceSynchronize()) return e;
     int *st = status_word();

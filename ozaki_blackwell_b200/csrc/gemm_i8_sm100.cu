@@ -64,14 +64,15 @@ __device__ __forceinline__ unsigned long long now_ns() {
 }
 // Bounded wait: each wait has its own budget, started the first time the spin loop looks at the clock. Returns false
 // when the budget ran out or another role of this CTA already gave up (*abort_flag != 0).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int who = 1) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int who = 1,
+                                          unsigned long long budget_ns = WAIT_NS) {
     unsigned long long deadline = 0;
     for (uint32_t spin = 0;; spin++) {
         if (mbar_try(bar, parity)) return true;
         if ((spin & 1023u) == 1023u) {
             if (*abort_flag) return false;
             const unsigned long long t = now_ns();
-            if (!deadline) deadline = t + WAIT_NS;
+            if (!deadline) deadline = t + budget_ns;
             else if (t > deadline) { *abort_flag = who; return false; }   // who: which wait gave up (diagnostics)
         }
     }
@@ -570,6 +571,20 @@ __global__ void __launch_bounds__(THREADS, 1) tensor_peak_probe(int iters, int *
     if (threadIdx.x == 0 && abort_flag) atomicCAS(status, 0, abort_flag);
 }
 
+
+// Self-test of the bounded wait: one CTA waits on a barrier that nothing will ever complete, with a short budget, and
+// must come back with the status word set instead of spinning. Nothing faults and nothing hangs.
+__global__ void wait_expiry_selftest(unsigned long long budget_ns, int *status) {
+    __shared__ __align__(8) unsigned long long bar_storage;
+    __shared__ int abort_flag;
+    const uint32_t bar = smem_u32(&bar_storage);
+    if (threadIdx.x == 0) { abort_flag = 0; mbar_init(bar, 1); asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+    __syncthreads();
+    const bool ok = mbar_wait(bar, 0, &abort_flag, 0x60, budget_ns);   // phase 0 never completes: nobody arrives
+    __syncthreads();
+    if (threadIdx.x == 0 && (!ok || abort_flag)) atomicCAS(status, 0, abort_flag ? abort_flag : 0x60);
+}
+
 }  // namespace g8
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -722,6 +737,13 @@ cudaError_t int8_peak_probe(int iters, int pair, float *ms, double *tops, int *s
     if (ms) *ms = t;
     if (tops) *tops = units * (double)iters * 8.0 * per_mma / (t * 1e-3) / 1e12;
     return cudaSuccess;
+}
+
+// launches the self-test above; the caller then reads the status word (expected: set)
+cudaError_t wait_expiry_selftest(unsigned budget_ms, int *status, cudaStream_t st) {
+    if (budget_ms == 0 || budget_ms > 2000) return cudaErrorInvalidValue;
+    g8::wait_expiry_selftest<<<1, 32, 0, st>>>((unsigned long long)budget_ms * 1000000ull, status);
+    return cudaGetLastError();
 }
 
 }  // namespace ozk

@@ -90,3 +90,35 @@ def test_partition_helpers():
         assert r[0][0] == 0 and r[-1][1] == n and len(r) <= max(p, 1)
         assert all(a[1] == b[0] for a, b in zip(r, r[1:]))
         assert all(lo % 256 == 0 for lo, _ in r) and all(hi > lo for lo, hi in r)
+
+
+def _worker_with_a_missing_rank(rank, world, port, out_dir):
+    """Rank 1 leaves before the product; rank 0's broadcast must end with an error after the group's short timeout."""
+    import datetime
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    from ozaki_blackwell_b200.dist import RowShardedGemm
+    if rank == 1:
+        os._exit(0)                                             # gone, between steps, with nothing of its own in flight
+    op = RowShardedGemm(4, 300, 32, 16, src=0, panels=2, engine=CheckerEngine(16), device="cpu")
+    a, b, c = torch.ones((4, 32), dtype=torch.float64), torch.ones((32, 300), dtype=torch.float64), torch.zeros((4, 300), dtype=torch.float64)
+    try:
+        op(a, b, c)
+        outcome = "completed"
+    except Exception as e:   # the failure surfaces on the host as an exception, not as a hang
+        outcome = "error: " + type(e).__name__
+    with open(os.path.join(out_dir, "outcome.txt"), "w") as f:
+        f.write(outcome)
+    os._exit(0)
+
+
+def test_a_vanished_rank_becomes_an_error_not_a_hang(tmp_path):
+    port = 31500 + (os.getpid() % 2000)
+    ctx = mp.get_context("spawn")
+    procs = [ctx.Process(target=_worker_with_a_missing_rank, args=(r, 2, port, str(tmp_path))) for r in range(2)]
+    [p.start() for p in procs]
+    for p in procs:
+        p.join(timeout=90)
+        assert not p.is_alive(), "a rank is still waiting for the one that left"
+    outcome = (tmp_path / "outcome.txt").read_text()
+    assert outcome.startswith("error"), outcome

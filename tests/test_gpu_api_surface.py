@@ -118,3 +118,16 @@ def test_cpp_program_against_the_header(tmp_path):
     assert r.returncode == 0 and r.stdout.startswith("ok"), r.stdout + r.stderr
     C = np.fromfile(tmp_path / "c.bin").reshape(M, N)
     assert g.same_bits(C, o.dgemm(A, B, nm))
+
+
+def test_an_expired_wait_is_reported_and_the_context_survives():
+    """The failure path of the GEMM kernel's bounded waits, without any fault: a wait that nothing will satisfy runs out of
+    its (short) budget, the status word is raised, the call returns OZB_ETIMEOUT, and the next product is correct."""
+    import gpu_util as g
+    from ozaki_blackwell_b200._lib import lib
+    assert lib.ozb_selftest_wait_expiry(50) == 10004
+    assert b"wait" in lib.ozb_error(10004)
+    assert lib.ozb_status() == 0                                  # reading the status cleared it
+    assert lib.ozb_selftest_wait_expiry(0) == 10001
+    A, B = g.synthetic(64, 96, 140), g.synthetic(96, 80, 141)
+    assert g.same_bits(g.gpu_dgemm(A, B, 16), o.dgemm(A, B, 16))
