@@ -173,37 +173,38 @@ __global__ void __launch_bounds__(256) x_residues(const uint16_t *__restrict__ X
 }
 
 // ---- 3b. residues of W' = (E4M3 2^9) * multiplier, written transposed (K contiguous) through shared memory ----
-constexpr int WT_COLS = 32, WT_K = 128, WT_PITCH = WT_K + 16;
-constexpr int WT_SMEM = NMAX * WT_COLS * WT_PITCH;
+// Block: 256 threads, tile of 128 columns x 32 k (inside one 128 x 128 scale block). Phase 1: lane = columns lane, lane +
+// 32, lane + 64, lane + 96 of the tile (every load instruction of a warp reads one 32-byte sector), warp w owns k in
+// [4w, 4w + 4): each thread forms four W' per column and parks their residues, four k to a word, in S[l][j][k], rows of
+// nine words (an odd pitch: neighbouring columns fall into different banks). Phase 2: eight threads per 32-byte row
+// write the tile out, a full sector per row.
+constexpr int WT_COLS = 128, WT_K = 32, WT_PITCH = WT_K + 4;
 __global__ void __launch_bounds__(256) w_residues_t(const uint8_t *__restrict__ W, int K, int N, long long ldw, const long long *__restrict__ mult,
                                                     int nbj, int nm, int8_t *__restrict__ Rp, int ld, size_t plane) {
     extern __shared__ __align__(16) uint8_t tile[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int j0 = blockIdx.x * WT_COLS, kb = blockIdx.y * WT_K;   // the tile lies inside one 128 x 128 scale block
-    const int j = j0 + lane, k0 = kb + warp * 16;
-    if (j < N) {
-        const long long mu = mult[(size_t)blockIdx.y * nbj + j / 128];
+    const int j0 = blockIdx.x * WT_COLS, kb = blockIdx.y * WT_K, k0 = kb + warp * 4;
+    const long long mu = mult[(size_t)(kb / 128) * nbj + j0 / 128];
 #pragma unroll
-        for (int q = 0; q < 4; q++) {
+    for (int c = 0; c < 4; c++) {
+        const int jj = lane + 32 * c, j = j0 + jj;
+        if (j < N) {
             long long v[4];
 #pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const int k = k0 + 4 * q + e;
-                v[e] = k < K ? (long long)decode_e4m3(W[(size_t)k * ldw + j]) * mu : 0;
-            }
+            for (int e = 0; e < 4; e++) v[e] = k0 + e < K ? (long long)decode_e4m3(W[(size_t)(k0 + e) * ldw + j]) * mu : 0;
             residues_of_4_n(v, nm, [&](int l, uint32_t word) {
-                *reinterpret_cast<uint32_t *>(tile + (l * WT_COLS + lane) * WT_PITCH + warp * 16 + 4 * q) = word;
+                *reinterpret_cast<uint32_t *>(tile + (l * WT_COLS + jj) * WT_PITCH + warp * 4) = word;
             });
         }
     }
     __syncthreads();
-    const int c = threadIdx.x & 7, kpos = kb + c * 16;
+    const int c = threadIdx.x & 7, kpos = kb + c * 4;
     if (kpos >= K) return;
-    for (int l = 0; l < nm; l++) {
-        const int jj = threadIdx.x >> 3;
+    for (int i = threadIdx.x >> 3; i < nm * WT_COLS; i += 32) {   // rows of the tile: (l, j)
+        const int l = i / WT_COLS, jj = i % WT_COLS;
         if (j0 + jj < N)
-            *reinterpret_cast<uint4 *>(Rp + (size_t)l * plane + (size_t)(j0 + jj) * ld + kpos) =
-                *reinterpret_cast<const uint4 *>(tile + (l * WT_COLS + jj) * WT_PITCH + c * 16);
+            *reinterpret_cast<uint32_t *>(Rp + (size_t)l * plane + (size_t)(j0 + jj) * ld + kpos) =
+                *reinterpret_cast<const uint32_t *>(tile + (l * WT_COLS + jj) * WT_PITCH + c * 4);
     }
 }
 
@@ -247,6 +248,7 @@ __device__ __forceinline__ bool sub_pow2(unsigned (&v)[NL], int d) {
     return c >= 0;
 }
 
+template <int LIMBS>   // limbs the product of the nm moduli needs: 4 up to 15 moduli (118 bits), 5 up to 19 (148 bits)
 __global__ void __launch_bounds__(128) crt_round(const int8_t *__restrict__ Cr, size_t plane, int M, int N, long long ldr, int nm,
                                                  const RowInfo *__restrict__ rinfo, const ColInfo *__restrict__ cinfo, float *__restrict__ Y,
                                                  long long ldy, int *__restrict__ open) {
@@ -271,7 +273,7 @@ __global__ void __launch_bounds__(128) crt_round(const int8_t *__restrict__ Cr, 
     float out[4];
 #pragma unroll 1
     for (int e = 0; e < 4; e++) {
-        unsigned long long acc[NL] = {};
+        unsigned long long acc[LIMBS] = {};
         long long qf = 0;
 #pragma unroll
         for (int l = 0; l < NMAX; l++) {
@@ -281,14 +283,16 @@ __global__ void __launch_bounds__(128) crt_round(const int8_t *__restrict__ Cr, 
                 if (r < 0) r += modulus(l);
                 qf += (long long)r * T.F[l];
 #pragma unroll
-                for (int k = 0; k < NL; k++) acc[k] += (unsigned long long)(unsigned)r * T.W[l][k];
+                for (int k = 0; k < LIMBS; k++) acc[k] += (unsigned long long)(unsigned)r * T.W[l][k];
             }
         }
         const long long q = (qf + (1ll << 39)) >> 40;
         long long c = 0;
-        unsigned v[NL];
+        unsigned v[NL];   // two's complement over LIMBS limbs, then sign-extended to NL for the shared rounding code
 #pragma unroll
-        for (int k = 0; k < NL; k++) { c += (long long)acc[k] - q * (long long)T.P[k]; v[k] = (unsigned)c; c >>= 32; }
+        for (int k = 0; k < LIMBS; k++) { c += (long long)acc[k] - q * (long long)T.P[k]; v[k] = (unsigned)c; c >>= 32; }
+#pragma unroll
+        for (int k = LIMBS; k < NL; k++) v[k] = (int)v[LIMBS - 1] < 0 ? 0xFFFFFFFFu : 0u;
         const bool neg = (int)v[NL - 1] < 0;
         if (neg) {
             unsigned long long b = 1;
@@ -419,10 +423,12 @@ int exact_bf16_fp8_gemm(int M, int N, int K, const uint16_t *X, long long ldx, c
         wk.nm = nm;
     }
     static PerDevice pd;
-    if (cudaError_t a = pd.once([] { return cudaFuncSetAttribute(w_residues_t, cudaFuncAttributeMaxDynamicSharedMemorySize, WT_SMEM); })) return (int)a;
+    if (cudaError_t a = pd.once([] { return cudaFuncSetAttribute(w_residues_t, cudaFuncAttributeMaxDynamicSharedMemorySize, NMAX * WT_COLS * WT_PITCH); }))
+        return (int)a;
     // 3. residues, GEMMs; 4. reconstruction and rounding
     x_residues<<<M, 256, 0, st>>>(X, K, ldx, wk.rinfo, nm, wk.Xr, Kp, (size_t)M * Kp);
-    w_residues_t<<<dim3((N + WT_COLS - 1) / WT_COLS, nbk), 256, WT_SMEM, st>>>(W, K, N, ldw, wk.mult, nbj, nm, wk.Wr, Kp, (size_t)N * Kp);
+    w_residues_t<<<dim3((N + WT_COLS - 1) / WT_COLS, (K + WT_K - 1) / WT_K), 256, nm * WT_COLS * WT_PITCH, st>>>(W, K, N, ldw, wk.mult, nbj, nm, wk.Wr,
+                                                                                                          Kp, (size_t)N * Kp);
     e = cudaGetLastError();
     {   // long K in chunks of about 8192, as in the FP64 product (later chunks add to the stored residues)
         const int chunks = K > 12288 ? (K + 8191) / 8192 : 1, kc = ((K + chunks - 1) / chunks + 127) / 128 * 128;
@@ -431,7 +437,8 @@ int exact_bf16_fp8_gemm(int M, int N, int K, const uint16_t *X, long long ldx, c
                                (size_t)M * Np, 1, 0, wk.status, 0, st, c > 0);
     }
     if (e) return (int)e;
-    crt_round<<<dim3(M, (N + 511) / 512), 128, 0, st>>>(wk.Cr, (size_t)M * Np, M, N, Np, nm, wk.rinfo, wk.cinfo, Y, ldy, wk.global + 2);
+    if (nm <= 15) crt_round<4><<<dim3(M, (N + 511) / 512), 128, 0, st>>>(wk.Cr, (size_t)M * Np, M, N, Np, nm, wk.rinfo, wk.cinfo, Y, ldy, wk.global + 2);
+    else crt_round<5><<<dim3(M, (N + 511) / 512), 128, 0, st>>>(wk.Cr, (size_t)M * Np, M, N, Np, nm, wk.rinfo, wk.cinfo, Y, ldy, wk.global + 2);
     e = cudaGetLastError();
     int hst[64] = {};
     if (!e) e = cudaMemcpyAsync(hg, wk.global, 16, cudaMemcpyDeviceToHost, st);
