@@ -46,50 +46,68 @@ def peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 200 ms while the timed region runs."""
-    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 20 ms. The sampler is started early (nvidia-smi
+    takes a moment to come up) and every sample carries a time stamp; only the samples that fall inside the timed region
+    [mark_start(), mark_end()] are summarised."""
+    Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
-        self.index, self.proc, self.path = index, None, None
+        self.index, self.proc, self.path, self.t0, self.t1 = index, None, None, None, None
 
     def start(self):
         try:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "200"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+                                          "-lms", "20"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+            for _ in range(100):                      # wait (at most 5 s) for the first sample
+                if os.path.getsize(self.path) > 0:
+                    break
+                time.sleep(0.05)
         except Exception:
             self.proc = None
 
+    def mark_start(self):
+        self.t0 = time.time()
+
+    def mark_end(self):
+        self.t1 = time.time()
+
     def stop(self):
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        import datetime
+        out = {"sm_mhz": None, "sm_max_mhz": None, "power_w": None, "reasons": [], "samples": 0}
         if not self.proc:
             return out
+        time.sleep(0.05)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
+        sm, mx, pw, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         try:
             for line in open(self.path):
                 f = [x.strip() for x in line.split(",")]
-                if len(f) < 7:
+                if len(f) < 8:
                     continue
                 try:
-                    sm.append(float(f[0])); mx.append(float(f[1]))
+                    ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                    c, m, p = float(f[1]), float(f[2]), float(f[3])
                 except ValueError:
                     continue
-                for nme, v in zip(names, f[3:7]):
+                if self.t0 is not None and not (self.t0 <= ts <= self.t1 + 0.02):
+                    continue
+                sm.append(c); mx.append(m); pw.append(p)
+                for nme, v in zip(names, f[4:8]):
                     if v.lower().startswith("active"):
                         reasons.add(nme)
             os.unlink(self.path)
         except Exception:
             pass
         if sm:
-            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), power_w=statistics.median(pw), reasons=sorted(reasons), samples=len(sm))
         return out
 
 
@@ -206,11 +224,13 @@ def run_ours(args):
         sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    sampler.mark_start()
     e0.record(stream)
     for _ in range(steps):
         op(A, B, C)
     e1.record(stream)
     barrier()
+    sampler.mark_end()
     clocks = sampler.stop() if rank == 0 else None
     op.engine.status()
     ms_total = e0.elapsed_time(e1)
@@ -324,7 +344,7 @@ def run_ours(args):
                        "moduli": nm, "n": n, "M_total": M * world, "l2": "operands (512 MiB each at n=8192) exceed L2; no flush needed",
                        "parallelism": f"row-block x{world}", "panels": len(op.ranges)},
             "gpu_launches": steps * (5 if world == 1 else 2 + 4 * len(op.ranges)),
-            "clocks": {k: clocks[k] for k in ("sm_mhz", "sm_max_mhz", "reasons")} if clocks else None,
+            "clocks": {k: clocks[k] for k in ("sm_mhz", "sm_max_mhz", "power_w", "reasons", "samples")} if clocks else None,
         }
         if e2e:
             line["e2e"] = e2e
@@ -344,7 +364,7 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--size", "--n", dest="n", type=int, default=8192, help="n of the n x n x n product (use --size under torchrun)")
