@@ -244,7 +244,10 @@ static int plan_dgemm_host(ozb_plan *p, const double *A, const double *B, double
         e = cudaMalloc(&p->hA, M * K * 8);
         if (!e) e = cudaMalloc(&p->hB, K * N * 8);
         if (!e) e = cudaMalloc(&p->hC, M * N * 8);
-        if (!e) e = cudaStreamCreateWithFlags(&p->sIn, cudaStreamNonBlocking);
+        if (e) return (int)e;
+    }
+    if (!p->sIn) {
+        e = cudaStreamCreateWithFlags(&p->sIn, cudaStreamNonBlocking);
         if (!e) e = cudaStreamCreateWithFlags(&p->sRun, cudaStreamNonBlocking);
         if (!e) e = cudaStreamCreateWithFlags(&p->sOut, cudaStreamNonBlocking);
         for (auto &ev : p->evIn) if (!e) e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
@@ -388,9 +391,37 @@ OZB_API int ozb_dgemm(int M, int N, int K, const double *A, const double *B, dou
         if (int e = finish()) return e;
         return plan_status(p);
     }
-    if (int e = plan_dgemm_host(p, A, B, C)) return e;
-    if (int e = finish()) return e;
-    return plan_status(p);
+    // Pinned (page-locked) host memory takes the overlapped path. Pageable memory cannot be copied asynchronously -- every
+    // piece would be staged by the driver in issue order -- so it is moved with three plain copies, as the reference does
+    // (python/capi.cu:37-48); OZ_HOST_PIPELINE=1 / 0 forces one or the other.
+    static const int force = [] { const char *env = getenv("OZ_HOST_PIPELINE"); return env && *env ? atoi(env) : -1; }();
+    bool pinned = false;
+    {
+        cudaPointerAttributes pa, pb, pc;
+        if (!cudaPointerGetAttributes(&pa, A) && !cudaPointerGetAttributes(&pb, B) && !cudaPointerGetAttributes(&pc, C))
+            pinned = pa.type == cudaMemoryTypeHost && pb.type == cudaMemoryTypeHost && pc.type == cudaMemoryTypeHost;
+        cudaGetLastError();
+    }
+    if (force == 1 || (force != 0 && pinned)) {
+        if (int e = plan_dgemm_host(p, A, B, C)) return e;
+        if (int e = finish()) return e;
+        return plan_status(p);
+    }
+    const size_t la = (size_t)M * K * 8, lb = (size_t)K * N * 8, lc = (size_t)M * N * 8;
+    int e = 0;
+    if (!p->hA) {
+        e = (int)cudaMalloc(&p->hA, la);
+        if (!e) e = (int)cudaMalloc(&p->hB, lb);
+        if (!e) e = (int)cudaMalloc(&p->hC, lc);
+        if (e) { cudaFree(p->hA); cudaFree(p->hB); cudaFree(p->hC); p->hA = p->hB = p->hC = nullptr; return e; }
+    }
+    e = (int)cudaMemcpy(p->hA, A, la, cudaMemcpyHostToDevice);
+    if (!e) e = (int)cudaMemcpy(p->hB, B, lb, cudaMemcpyHostToDevice);
+    if (!e) e = plan_dgemm(p, p->hA, K, p->hB, N, p->hC, N, 0);
+    if (!e) e = finish();
+    if (!e) e = plan_status(p);
+    if (!e) e = (int)cudaMemcpy(C, p->hC, lc, cudaMemcpyDeviceToHost);
+    return e;
 }
 
 OZB_API int ozb_ddgemm(int M, int N, int K, const double *Ah, const double *Al, const double *Bh, const double *Bl, double *Ch,
