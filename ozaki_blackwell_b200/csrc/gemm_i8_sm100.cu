@@ -656,7 +656,13 @@ cudaError_t gemm_i8_planes(const int8_t *A, const int8_t *Bt, void *C, int M, in
     p.M = M; p.N = N; p.K = K; p.Z = Z;
     p.tiles_m = (M + g8::BM - 1) / g8::BM;
     p.tiles_n = (N + g8::BN - 1) / g8::BN;
-    p.band = 8;
+    // band height in tile rows (OZ_BAND overrides, as in the reference, src/gemm_i8.cuh:149). Measured on B200 with the
+    // two-CTA kernel: 16 beats 8 by 5-8 % at n = 16384 and 32768 (B is re-read from HBM once per band) and is no worse at
+    // n = 8192; 32 is slower again (the working set of one wave of tiles grows past what L2 serves best).
+    {
+        static const int env_band = [] { const char *e = getenv("OZ_BAND"); return e && *e ? atoi(e) : 0; }();
+        p.band = env_band > 0 ? env_band : 16;
+    }
     p.first_modulus = first_modulus;
     p.accumulate = accumulate;
     p.C = C; p.ldc = ldc; p.plane_c = pc; p.status = status;
