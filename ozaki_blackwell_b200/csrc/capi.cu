@@ -146,7 +146,8 @@ static int plan_make(int M, int N, int K, int nm, int maxbits, ozb_plan **out) {
 // POP/s, the kernel turns HBM-bound); later chunks add to the residues the earlier ones stored.
 static cudaError_t gemm_chunks(ozb_plan *p, const int8_t *Br, int8_t *Cr, int n, cudaStream_t st, int i0 = 0, int m = -1) {
     if (m < 0) m = p->M;   // rows [i0, i0 + m) of A and C
-    const int chunks = p->K > 12288 ? (p->K + 8191) / 8192 : 1;
+    static const int target = [] { const char *env = getenv("OZ_KCHUNK"); const int v = env && *env ? atoi(env) : 0; return v >= 1024 ? v : 8192; }();
+    const int chunks = p->K > target + target / 2 ? (p->K + target - 1) / target : 1;
     const int kc = round_up((p->K + chunks - 1) / chunks, 128);
     for (int k0 = 0, i = 0; k0 < p->K; k0 += kc, i++) {
         const int klen = p->K - k0 < kc ? p->K - k0 : kc;
