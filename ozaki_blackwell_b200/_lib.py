@@ -7,7 +7,7 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libozaki_blackwell.so")
+LIB_PATH = os.environ.get("OZB_LIBRARY") or os.path.join(_HERE, "libozaki_blackwell.so")   # OZB_LIBRARY: another build of the same ABI
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(f"{LIB_PATH} is missing: build it with `make -C {os.path.join(_HERE, 'csrc')}`; there is no fallback path")

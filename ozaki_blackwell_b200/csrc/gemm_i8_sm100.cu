@@ -302,7 +302,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_i8_tc(const __grid_constant__
 // ---------------------------------------------------------------------------------------------------------------
 // Two-CTA variant (cta_group::2): a cluster of two CTAs on one TPC works on one 256 x 256 tile.
 // Each CTA loads its own 128 rows of A and its own 128 of the 256 rows of Bt (half the shared-memory fill and read
-// traffic per tensor operation of the one-CTA kernel, so 6 stages of 32 KB fit instead of 4 of 48 KB); the leader CTA
+// traffic per tensor operation of the one-CTA kernel, so 7 stages of 32 KB fit instead of 4 of 48 KB); the leader CTA
 // (cluster rank 0) issues tcgen05.mma.cta_group::2 with M = 256, and every CTA finds its 128 rows of the accumulator in
 // its own tensor memory. Signals cross the pair like this:
 //   full[s]      lives in the leader: its producer expects the bytes of both CTAs, and both producers point their TMA
@@ -315,7 +315,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_i8_tc(const __grid_constant__
 // ---------------------------------------------------------------------------------------------------------------
 namespace two {
 constexpr int BM2 = 256;                            // rows of A per pair (128 per CTA)
-constexpr int STAGES2 = 6;
+constexpr int STAGES2 = 7;
 constexpr int HALF_B = (BN / 2) * BKB;              // this CTA's 128 rows of Bt per stage
 constexpr int STAGE2_BYTES = A_BYTES + HALF_B;      // 16 KB + 16 KB
 constexpr int SMEM2_BYTES = STAGES2 * STAGE2_BYTES + 1024 + 256;
