@@ -352,7 +352,7 @@ def run_ours(args):
             line["roofline"] = roof
             line["phases_ms"] = {"before_first_gemm": float(phases[0]), "gemm_i8_kernels": float(phases[1]),
                                  "after_last_gemm": float(phases[2]), "product": float(phases[3]),
-                                 "note": "column panels overlap B's residues, GEMMs and CRT on three streams"}
+                                 "note": "CUDA events recorded by the library on the launching stream inside the timed steps (mean over the steps)"}
         if cpu:
             line["cpu_baseline"] = cpu
         print(json.dumps(line))

@@ -49,8 +49,13 @@ __device__ __forceinline__ void residues_of_4(const long long (&v)[4], Put &&put
 // ---------------------------------------------------------------------------------------------------------------
 // A side: one block per row. R chunks of four doubles per thread stay in registers between the two phases.
 // ---------------------------------------------------------------------------------------------------------------
+#ifndef OZ_ROW_R
+#define OZ_ROW_R 4      // chunks of four doubles a thread keeps in registers
+#define OZ_ROW_T 256    // largest block
+#define OZ_ROW_MINB 4   // blocks per SM the register allocation must allow
+#endif
 template <int NM, int R, int MAXT, bool GIVEN = false>   // GIVEN: the scales are already in s_out (2-norm mode), no max pass
-__global__ void __launch_bounds__(MAXT) row_scale_residues(const double *__restrict__ X, int len, long long ldx, int bits,
+__global__ void __launch_bounds__(MAXT, OZ_ROW_MINB) row_scale_residues(const double *__restrict__ X, int len, long long ldx, int bits,
                                                            int *__restrict__ s_out, int8_t *__restrict__ Rp, int ld,
                                                            size_t plane) {
     const int r = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
@@ -169,8 +174,11 @@ __global__ void __launch_bounds__(256) col_absmax(const double *__restrict__ X, 
 constexpr int CT_COLS = 32, CT_K = 128, CT_PITCH = CT_K + 16;
 template <int NM> constexpr int col_tile_smem() { return NM * CT_COLS * CT_PITCH; }
 
+#ifndef OZ_COL_MINB
+#define OZ_COL_MINB 3   // measured on B200: 3 blocks per SM (80 registers, a 40-byte spill) 0.511 ms, 2 blocks 0.545 ms, 4 blocks 0.530 ms at n = 8192
+#endif
 template <int NM>
-__global__ void __launch_bounds__(256) col_residues_t(const double *__restrict__ X, int rows, int cols, long long ldx,
+__global__ void __launch_bounds__(256, OZ_COL_MINB) col_residues_t(const double *__restrict__ X, int rows, int cols, long long ldx,
                                                       const unsigned long long *__restrict__ colmax, int bits,
                                                       int *__restrict__ s_out, int8_t *__restrict__ Rp, int ld, size_t plane) {
     extern __shared__ __align__(16) uint8_t tile[];
@@ -275,11 +283,14 @@ __global__ void __launch_bounds__(256) scales_norm_kernel(const double *__restri
 template <int NM>
 static cudaError_t launch_rows_t(const double *X, int rows, int len, long long ldx, int bits, int *s, int8_t *R, int ld,
                                  size_t plane, cudaStream_t st) {
-    constexpr int RR = 8, MAXT = 512;           // 64 registers of row data per thread, 128 allowed
+    // Rows of up to 4096 entries stay in registers (4 chunks x 256 threads); longer ones are read a second time, from L2.
+    // Measured on B200 at K = 8192: this shape (64 registers, 4 blocks per SM) takes 0.427 ms, keeping the whole row in
+    // registers (8 chunks, 100 registers, 2 blocks per SM) 0.456 ms: occupancy matters more than the second read.
+    constexpr int RR = OZ_ROW_R, MAXT = OZ_ROW_T;
     int nt = ((len + 3) / 4 + RR - 1) / RR;     // threads that hold the row in registers
     nt = (nt + 31) / 32 * 32;
     if (nt < 32) nt = 32;
-    if (nt > MAXT) nt = MAXT;                   // longer rows (K > 16384) are read twice; the second read mostly hits L2
+    if (nt > MAXT) nt = MAXT;
     row_scale_residues<NM, RR, MAXT><<<rows, nt, 0, st>>>(X, len, ldx, bits, s, R, ld, plane);
     return cudaGetLastError();
 }
@@ -311,7 +322,7 @@ cudaError_t cols_residues_from_max(int nm, const double *X, int rows, int cols, 
 template <int NM>
 static cudaError_t launch_rows_given_t(const double *X, int rows, int len, long long ldx, int *s, int8_t *R, int ld, size_t plane,
                                        cudaStream_t st) {
-    constexpr int RR = 8, MAXT = 512;
+    constexpr int RR = OZ_ROW_R, MAXT = OZ_ROW_T;
     int nt = ((len + 3) / 4 + RR - 1) / RR;
     nt = (nt + 31) / 32 * 32;
     if (nt < 32) nt = 32;
