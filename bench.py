@@ -203,7 +203,7 @@ def run_ours(args):
     B = synthetic(K, N, 7, dev) if rank == 0 else None
     C = torch.empty((M, N), dtype=torch.float64, device=dev)
     stream = torch.cuda.current_stream()
-    op = RowShardedGemm(M, N, K, nm, panels=args.panels)
+    op = RowShardedGemm(M, N, K, nm, panels=args.panels, layout=args.layout)
     plan = op.engine._plan
     steps, warm = args.steps, args.warmup
     check(lib.ozb_plan_profile(plan, steps if world == 1 else 0))
@@ -342,8 +342,8 @@ def run_ours(args):
             "config": {"workload": f"FP64 GEMM n={n}, {nm} moduli (Ozaki-II), entries U[-1,1)*2^e, e in [-8,8]"
                                    + ("" if world == 1 else f"; {world} row blocks of {M} rows (M={M * world}), B broadcast from rank 0 every step"),
                        "moduli": nm, "n": n, "M_total": M * world, "l2": "operands (512 MiB each at n=8192) exceed L2; no flush needed",
-                       "parallelism": f"row-block x{world}", "panels": len(op.ranges)},
-            "gpu_launches": steps * (5 if world == 1 else 2 + 4 * len(op.ranges)),
+                       "parallelism": f"row-block x{world}", "panels": len(op.ranges), "broadcast_layout": op.layout if world > 1 else None},
+            "gpu_launches": steps * (5 if world == 1 else (4 + len(op.ranges) if op.layout == "rows" else 2 + 4 * len(op.ranges))),
             "clocks": {k: clocks[k] for k in ("sm_mhz", "sm_max_mhz", "power_w", "reasons", "samples")} if clocks else None,
         }
         if e2e:
@@ -369,7 +369,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--size", "--n", dest="n", type=int, default=8192, help="n of the n x n x n product (use --size under torchrun)")
     ap.add_argument("--moduli", type=int, default=16)
-    ap.add_argument("--panels", type=int, default=4)
+    ap.add_argument("--panels", type=int, default=4, help="pieces B is broadcast in (N > 1)")
+    ap.add_argument("--layout", choices=("rows", "panels"), default="panels", help="broadcast B in row chunks or in column panels (N > 1)")
     ap.add_argument("--strong", action="store_true", help="strong scaling: the n x n x n product is split over the ranks")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--cpu-rows", type=int, default=256)

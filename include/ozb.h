@@ -85,6 +85,14 @@ int ozb_plan_dgemm(ozb_plan *p, const double *A, long long lda, const double *B,
  * the panel's first column. */
 int ozb_plan_set_a(ozb_plan *p, const double *A, long long lda, void *stream);
 int ozb_plan_panel(ozb_plan *p, const double *B, long long ldb, double *C, long long ldc, int j0, int ncols, void *stream);
+/* The same product with B delivered in chunks of rows (a broadcast or a host transfer in flight): ozb_plan_b_begin once,
+ * ozb_plan_b_rows for every chunk in any order (it only accumulates the column maxima of those rows), ozb_plan_b_finish
+ * with the complete B (forms the residues), then ozb_plan_multiply with the A given to ozb_plan_set_a. The prepared
+ * operands stay valid, so one B can be multiplied by several A (call ozb_plan_set_a and ozb_plan_multiply again). */
+int ozb_plan_b_begin(ozb_plan *p, void *stream);
+int ozb_plan_b_rows(ozb_plan *p, const double *Brows, long long ldb, int rows, void *stream);
+int ozb_plan_b_finish(ozb_plan *p, const double *B, long long ldb, void *stream);
+int ozb_plan_multiply(ozb_plan *p, double *C, long long ldc, void *stream);
 /* Workspace view, for stage-by-stage checks against the reference's Plan fields (src/ozaki2.cuh:117-119):
  * Ar [nm][M][Kp] int8, Br [nm][N][Kp] int8, Cr [nm][M][Np] int8 (balanced residues of the products, where the
  * reference keeps int32 Cl), sa [M], sb [N]. */

@@ -584,6 +584,32 @@ OZB_API int ozb_plan_panel(ozb_plan *p, const double *B, long long ldb, double *
     std::lock_guard<std::mutex> g(mu);
     return plan_panel(p, B, ldb, C, ldc, j0, ncols, (cudaStream_t)stream, nullptr);
 }
+// B in chunks of rows (as it arrives from a broadcast or from the host), then the product with the prepared operands
+OZB_API int ozb_plan_b_begin(ozb_plan *p, void *stream) {
+    if (!p) return OZB_EARG;
+    std::lock_guard<std::mutex> g(mu);
+    p->last = (cudaStream_t)stream;
+    return (int)cudaMemsetAsync(p->colmax, 0, (size_t)p->N * 8, (cudaStream_t)stream);
+}
+OZB_API int ozb_plan_b_rows(ozb_plan *p, const double *Brows, long long ldb, int rows, void *stream) {
+    if (!p || !Brows || rows <= 0 || rows > p->K || ldb < p->N) return OZB_EARG;
+    std::lock_guard<std::mutex> g(mu);
+    return (int)cols_absmax_accumulate(Brows, rows, p->N, ldb, p->colmax, (cudaStream_t)stream);
+}
+OZB_API int ozb_plan_b_finish(ozb_plan *p, const double *B, long long ldb, void *stream) {
+    if (!p || !B || ldb < p->N) return OZB_EARG;
+    std::lock_guard<std::mutex> g(mu);
+    return (int)cols_residues_from_max(p->nm, B, p->K, p->N, ldb, p->bits, p->colmax, p->sb, p->Br, p->Kp, p->planeB, (cudaStream_t)stream);
+}
+OZB_API int ozb_plan_multiply(ozb_plan *p, double *C, long long ldc, void *stream) {
+    if (!p || !C || ldc < p->N) return OZB_EARG;
+    std::lock_guard<std::mutex> g(mu);
+    cudaStream_t st = (cudaStream_t)stream;
+    p->last = st;
+    cudaError_t e = gemm_chunks(p, p->Br, p->Cr, p->N, st);
+    if (!e) e = crt_from_i8(p->nm, p->Cr, p->planeC, p->M, p->N, p->Np, p->sa, p->sb, C, ldc, st);
+    return (int)e;
+}
 OZB_API int ozb_plan_view(ozb_plan *p, int *bits, int *Kp, int *Np, int8_t **Ar, int8_t **Br, int8_t **Cr, int **sa, int **sb) {
     if (!p) return OZB_EARG;
     if (bits) *bits = p->bits;

@@ -2,7 +2,7 @@
 
 The product path has no CPU implementation, so the ranks here get an engine that answers set_a / panel / full with the
 CPU checker; what is under test is the host logic of ozaki_blackwell_b200/dist.py: the partition of rows, the panel
-ranges, that every rank receives every panel of B from the source rank, and that the assembled result is bit-identical
+ranges and row chunks, that every rank receives every piece of B from the source rank, and that the assembled result is bit-identical
 to the unsharded product.
 """
 import os
@@ -33,12 +33,27 @@ class CheckerEngine:
         self.calls.append((j0, ncols))
         c[:, j0:j0 + ncols] = torch.from_numpy(o.dgemm(self.A, b_panel.numpy(), self.nm))
 
+    def b_begin(self, stream):
+        self.rows, self.B = [], None
+
+    def b_rows(self, rows, stream):
+        self.rows.append(rows.numpy().copy())
+
+    def b_finish(self, b, stream):
+        self.B = b.numpy().copy()
+        assert np.array_equal(np.vstack(self.rows), self.B)     # the chunks that arrived are the whole of B, in order
+        self.calls.append((len(self.rows), self.B.shape[0]))
+
+    def multiply(self, c, stream):
+        import oracle_lib as o
+        c.copy_(torch.from_numpy(o.dgemm(self.A, self.B, self.nm)))
+
     def full(self, a, b, c, stream):
         import oracle_lib as o
         c.copy_(torch.from_numpy(o.dgemm(a.numpy(), b.numpy(), self.nm)))
 
 
-def _worker(rank, world, port, M, N, K, nm, panels, src, out_dir):
+def _worker(rank, world, port, M, N, K, nm, panels, src, layout, out_dir):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     from ozaki_blackwell_b200.dist import RowShardedGemm, row_block
@@ -50,7 +65,7 @@ def _worker(rank, world, port, M, N, K, nm, panels, src, out_dir):
     b = torch.from_numpy(B.copy()) if rank == src else None     # only the source rank holds B
     c_local = torch.zeros((hi - lo, N), dtype=torch.float64)
     eng = CheckerEngine(nm)
-    op = RowShardedGemm(hi - lo, N, K, nm, src=src, panels=panels, engine=eng, device="cpu")
+    op = RowShardedGemm(hi - lo, N, K, nm, src=src, panels=panels, engine=eng, device="cpu", layout=layout)
     op(a_local, b, c_local)
     op(a_local, b, c_local)                                     # a second call reuses the staging buffers
     np.save(os.path.join(out_dir, f"c{rank}.npy"), c_local.numpy())
@@ -59,13 +74,14 @@ def _worker(rank, world, port, M, N, K, nm, panels, src, out_dir):
     dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("layout", ["rows", "panels"])
 @pytest.mark.parametrize("src", [0, 1])
-def test_two_ranks_match_the_unsharded_product(tmp_path, src):
+def test_two_ranks_match_the_unsharded_product(tmp_path, src, layout):
     import oracle_lib as o
     from ozaki_blackwell_b200.dist import panel_ranges, row_block
     M, N, K, nm, panels, world = 37, 600, 96, 16, 3, 2
-    port = 29500 + (os.getpid() % 2000) + src
-    mp.spawn(_worker, args=(world, port, M, N, K, nm, panels, src, str(tmp_path)), nprocs=world, join=True)
+    port = 29500 + (os.getpid() % 2000) + src + 2 * (layout == "rows")
+    mp.spawn(_worker, args=(world, port, M, N, K, nm, panels, src, layout, str(tmp_path)), nprocs=world, join=True)
     rng = np.random.default_rng(123)
     A = rng.uniform(-1, 1, (M, K)) * 2.0 ** rng.integers(-8, 9, (M, K))
     B = rng.uniform(-1, 1, (K, N)) * 2.0 ** rng.integers(-8, 9, (K, N))
@@ -74,7 +90,10 @@ def test_two_ranks_match_the_unsharded_product(tmp_path, src):
     assert np.array_equal(got.view(np.uint64), want.view(np.uint64))
     for r in range(world):
         calls = [tuple(c) for c in np.load(tmp_path / f"calls{r}.npy")]
-        assert calls == [(lo, hi - lo) for lo, hi in panel_ranges(N, panels)] * 2
+        if layout == "panels":
+            assert calls == [(lo, hi - lo) for lo, hi in panel_ranges(N, panels)] * 2
+        else:
+            assert calls == [(panels, K)] * 2
     assert row_block(M, 0, world) == (0, 19) and row_block(M, 1, world) == (19, 37)
 
 

@@ -52,6 +52,22 @@ def test_plan_interface_with_leading_dimensions_and_a_stream():
     g.check(lib.ozb_plan_status(plan))
     assert g.same_bits(Cd[:, :N].cpu().numpy(), want)
     assert lib.ozb_plan_panel(plan, g.ptr(Bd), ldb, g.ptr(Cd), ldc, 100, 50, None) == 10001    # panels start on multiples of 256
+    # B in chunks of rows, delivered out of order; then the prepared B with a second A
+    Cd.fill_(0)
+    g.check(lib.ozb_plan_b_begin(plan, None))
+    for k0, rows in ((200, K - 200), (0, 77), (77, 123)):
+        g.check(lib.ozb_plan_b_rows(plan, ctypes.c_void_p(Bd.data_ptr() + 8 * ldb * k0), ldb, rows, None))
+    g.check(lib.ozb_plan_b_finish(plan, g.ptr(Bd), ldb, None))
+    g.check(lib.ozb_plan_multiply(plan, g.ptr(Cd), ldc, None))
+    g.check(lib.ozb_plan_status(plan))
+    assert g.same_bits(Cd[:, :N].cpu().numpy(), want)
+    A2 = g.synthetic(M, K, 103)
+    Ad[:, :K] = g.dev(A2)
+    g.check(lib.ozb_plan_set_a(plan, g.ptr(Ad), lda, None))
+    g.check(lib.ozb_plan_multiply(plan, g.ptr(Cd), ldc, None))
+    g.check(lib.ozb_plan_status(plan))
+    assert g.same_bits(Cd[:, :N].cpu().numpy(), o.dgemm(A2, B, nm))
+    assert lib.ozb_plan_b_rows(plan, g.ptr(Bd), ldb, K + 1, None) == 10001
     lib.ozb_plan_destroy(plan)
 
 

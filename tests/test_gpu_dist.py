@@ -10,7 +10,7 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _worker(rank, world, port, M, N, K, nm, src, out_dir):
+def _worker(rank, world, port, M, N, K, nm, src, layout, out_dir):
     import torch
     import torch.distributed as dist
     sys.path.insert(0, HERE)
@@ -25,7 +25,7 @@ def _worker(rank, world, port, M, N, K, nm, src, out_dir):
     a = torch.from_numpy(A[lo:hi].copy()).cuda()
     b = torch.from_numpy(B).cuda() if rank == src else None
     c = torch.zeros((hi - lo, N), dtype=torch.float64, device="cuda")
-    op = RowShardedGemm(hi - lo, N, K, nm, src=src, panels=3)
+    op = RowShardedGemm(hi - lo, N, K, nm, src=src, panels=3, layout=layout)
     for _ in range(2):
         op(a, b, c)
     torch.cuda.synchronize()
@@ -35,16 +35,17 @@ def _worker(rank, world, port, M, N, K, nm, src, out_dir):
     dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("layout", ["rows", "panels"])
 @pytest.mark.parametrize("src", [0, 1])
-def test_two_gpus_bit_identical_to_one(tmp_path, src):
+def test_two_gpus_bit_identical_to_one(tmp_path, src, layout):
     import torch
     import torch.multiprocessing as mp
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import gpu_util as g
     M, N, K, nm = 700, 1000, 520, 16
-    port = 29600 + (os.getpid() % 1000) + src
-    mp.spawn(_worker, args=(2, port, M, N, K, nm, src, str(tmp_path)), nprocs=2, join=True)
+    port = 29600 + (os.getpid() % 1000) + src + 2 * (layout == "rows")
+    mp.spawn(_worker, args=(2, port, M, N, K, nm, src, layout, str(tmp_path)), nprocs=2, join=True)
     A, B = g.synthetic(M, K, 61), g.synthetic(K, N, 62)
     want = g.gpu_dgemm(A, B, nm)
     got = np.vstack([np.load(tmp_path / f"c{r}.npy") for r in range(2)])
