@@ -369,8 +369,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--size", "--n", dest="n", type=int, default=8192, help="n of the n x n x n product (use --size under torchrun)")
     ap.add_argument("--moduli", type=int, default=16)
-    ap.add_argument("--panels", type=int, default=4, help="pieces B is broadcast in (N > 1)")
-    ap.add_argument("--layout", choices=("rows", "panels"), default="panels", help="broadcast B in row chunks or in column panels (N > 1)")
+    ap.add_argument("--panels", type=int, default=None, help="pieces B is broadcast in (N > 1; default: by the size of B)")
+    ap.add_argument("--layout", choices=("auto", "rows", "panels"), default="auto", help="broadcast B in row chunks or in column panels (N > 1)")
     ap.add_argument("--strong", action="store_true", help="strong scaling: the n x n x n product is split over the ranks")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--cpu-rows", type=int, default=256)

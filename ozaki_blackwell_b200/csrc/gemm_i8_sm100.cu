@@ -15,11 +15,14 @@
 //   warps 2-5 epilogue: tcgen05.ld the finished accumulator (one row per thread), reduce mod m_z (or keep int32) and
 //            store, while the issuer is already accumulating the next tile into the other buffer.
 // Work items are (plane, tile) pairs walked plane by plane and, inside a plane, in bands of tile rows so that the A
-// band and the B panels in flight stay in L2. Every mbarrier wait is bounded: on expiry the CTA raises a status word,
+// band and the B panels in flight stay in L2. The two-CTA kernel hands them out dynamically (a device-wide counter read
+// by one otherwise idle warp per pair, a few items ahead), so pairs that run faster, or start earlier because the SMs of
+// others are still held by another kernel, take more of them. Every mbarrier wait is bounded: on expiry the CTA raises a status word,
 // stops issuing, releases its tensor memory and returns.
 #include <cuda.h>
 #include <cstdio>
 #include <cstdlib>
+#include <mutex>
 #include "oz_common.cuh"
 
 namespace ozk {
@@ -117,6 +120,7 @@ struct Params {
     long long ldc;                // row pitch of C in elements
     size_t plane_c;               // plane pitch of C in elements
     int *status;                  // device word: set to 1 when a wait timed out
+    int *counter;                 // two-CTA kernel: next work item, zeroed before the launch
 };
 
 struct ModTable { ModConsts v[MAXM]; };
@@ -319,6 +323,9 @@ constexpr int STAGES2 = 7;
 constexpr int HALF_B = (BN / 2) * BKB;              // this CTA's 128 rows of Bt per stage
 constexpr int STAGE2_BYTES = A_BYTES + HALF_B;      // 16 KB + 16 KB
 constexpr int SMEM2_BYTES = STAGES2 * STAGE2_BYTES + 1024 + 256;
+constexpr int WORK_SLOTS = 4;                       // work items handed out ahead of their use
+constexpr int WORK_READERS = 11;                    // per pair: two producers, one issuer, eight epilogue warps
+static_assert(8 * (2 * STAGES2 + 5 + 2 * WORK_SLOTS) + 4 * WORK_SLOTS <= 256, "barrier area");
 constexpr uint32_t IDESC2 = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM2 >> 4) << 24);
 }  // namespace two
 
@@ -338,6 +345,30 @@ __device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t bar, uint32_t by
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
     // default semantics (release at CTA scope): a cluster-scope release here stalled the arriving thread for ~1400 cycles
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_release_cluster(uint32_t bar) {   // orders this thread's earlier writes, remote ones included
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_acquire_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_acquire_cluster(uint32_t bar, uint32_t parity, volatile int *abort_flag, int who) {
+    unsigned long long deadline = 0;
+    for (uint32_t spin = 0;; spin++) {
+        if (mbar_try_acquire_cluster(bar, parity)) return true;
+        if ((spin & 1023u) == 1023u) {
+            if (*abort_flag) return false;
+            const unsigned long long t = now_ns();
+            if (!deadline) deadline = t + WAIT_NS;
+            else if (t > deadline) { *abort_flag = who; return false; }
+        }
+    }
 }
 __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap *map, int c0, int c1, int c2, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
@@ -370,6 +401,9 @@ gemm_i8_tc2(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
     auto accfull_bar = [&](int a) { return bars + 8u * (2 * STAGES2 + a); };
     auto accempty_bar = [&](int a) { return bars + 8u * (2 * STAGES2 + 2 + a); };
     const uint32_t tmem_slot = bars + 8u * (2 * STAGES2 + 4);
+    auto work_bar = [&](int s) { return bars + 8u * (2 * STAGES2 + 5 + s); };            // "slot s of the work ring is filled"
+    auto taken_bar = [&](int s) { return bars + 8u * (2 * STAGES2 + 5 + WORK_SLOTS + s); };  // "every role has read slot s" (CTA 1's is used)
+    const uint32_t work_ring = bars + 8u * (2 * STAGES2 + 5 + 2 * WORK_SLOTS);
     __shared__ int abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -378,6 +412,7 @@ gemm_i8_tc2(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
         abort_flag = 0;
         for (int s = 0; s < STAGES2; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (int a = 0; a < 2; a++) { mbar_init(accfull_bar(a), 1); mbar_init(accempty_bar(a), 8); }
+        for (int s = 0; s < WORK_SLOTS; s++) { mbar_init(work_bar(s), 1); mbar_init(taken_bar(s), WORK_READERS); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {   // warp 1 of both CTAs allocates together
@@ -398,6 +433,16 @@ gemm_i8_tc2(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
     const int kblocks = (p.K + BKB - 1) / BKB;
     const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
     volatile int *abortp = &abort_flag;
+    (void)pair; (void)npairs;
+    // next work item of this pair, -1 when there is none left: read from the ring the scheduler fills (below)
+    auto next_work = [&](uint32_t n, int who) -> int {
+        const int s = n % WORK_SLOTS;
+        if (!mbar_wait_acquire_cluster(work_bar(s), (n / WORK_SLOTS) & 1u, abortp, who)) return -1;
+        int w;
+        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(w) : "r"(work_ring + 4u * s) : "memory");
+        return w;
+    };
+    auto work_taken = [&](uint32_t n) { mbar_arrive_cluster(map_to_cta(taken_bar(n % WORK_SLOTS), 1)); };
 #ifdef OZ_TIMING
     long long t_wait = 0, t_all = clock64();
 #define OZ_T0 const long long t0_ = clock64();
@@ -410,7 +455,10 @@ gemm_i8_tc2(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
     if (warp == 0) {
         if (lane == 0) {
             uint32_t it = 0;
-            for (int w = pair; w < total && !*abortp; w += npairs) {
+            for (uint32_t n = 0; !*abortp; n++) {
+                const int w = next_work(n, 0x60 + (int)rank);
+                work_taken(n);
+                if (w < 0) break;
                 int z, tm, tn;
                 decode_work(pp, w, z, tm, tn);
                 for (int kb = 0; kb < kblocks; kb++, it++) {
@@ -431,8 +479,11 @@ gemm_i8_tc2(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
         }
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) {
-            uint32_t it = 0, n = 0;
-            for (int w = pair; w < total && !*abortp; w += npairs, n++) {
+            uint32_t it = 0;
+            for (uint32_t n = 0; !*abortp; n++) {
+                const int w = next_work(n, 0x62);
+                work_taken(n);
+                if (w < 0) break;
                 const uint32_t acc = n & 1u;
                 if (!mbar_wait(accempty_bar(acc), ((n >> 1) & 1u) ^ 1u, abortp, 0x20 + ((int)(n & 0xfff) << 8))) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -453,12 +504,30 @@ gemm_i8_tc2(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
                 if (!ok) break;
                 mma_commit_pair(accfull_bar(acc));
             }
+        } else if (lane == 0) {
+            // The peer's otherwise idle warp hands out the work: item n of this pair is whatever the device-wide counter
+            // says when the ring has room for it, so a pair that starts late (its SMs still busy with another kernel)
+            // or runs slowly simply takes fewer items. The first item needs no round trip to memory.
+            for (uint32_t n = 0; !*abortp; n++) {
+                const int s = n % WORK_SLOTS;
+                if (!mbar_wait(taken_bar(s), ((n / WORK_SLOTS) & 1u) ^ 1u, abortp, 0x70)) break;
+                int w = n == 0 ? pair : npairs + atomicAdd(p.counter, 1);
+                if (w >= total) w = -1;
+                asm volatile("st.shared.b32 [%0], %1;" ::"r"(work_ring + 4u * s), "r"(w) : "memory");
+                asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(map_to_cta(work_ring + 4u * s, 0)), "r"(w) : "memory");
+                mbar_arrive_release_cluster(map_to_cta(work_bar(s), 0));
+                mbar_arrive(work_bar(s));
+                if (w < 0) break;
+            }
         }
     } else {
         const int q = warp & 3;
         ModConsts mc{};
-        uint32_t n = 0;
-        for (int w = pair; w < total && !*abortp; w += npairs, n++) {
+        for (uint32_t n = 0; !*abortp; n++) {
+            const int w = next_work(n, 0x64 + (int)rank);
+            __syncwarp();
+            if (lane == 0) work_taken(n);
+            if (__any_sync(~0u, w < 0)) break;
             int z, tm, tn;
             decode_work(pp, w, z, tm, tn);
             const uint32_t acc = n & 1u;
@@ -633,6 +702,26 @@ static cudaError_t gemm_setup() {   // the kernels' shared-memory opt-in, on eve
     });
 }
 
+// Work counters of the two-CTA kernel. Every launch gets its own, zeroed on the launch's stream just before the kernel, so
+// launches that run at the same time on different streams never share one. They come round-robin from a fixed array in
+// the device image (nothing is allocated); one is handed out again after WORK_COUNTERS further launches on the device.
+constexpr int WORK_COUNTERS = 4096;
+static __device__ int g_work_counters[WORK_COUNTERS];
+static int *next_work_counter() {
+    static int *base[64] = {};
+    static unsigned next[64] = {};
+    static std::mutex m;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> g(m);
+    if (!base[dev]) {
+        void *ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_work_counters) != cudaSuccess || !ptr) { cudaGetLastError(); return nullptr; }
+        base[dev] = static_cast<int *>(ptr);
+    }
+    return base[dev] + (next[dev]++ % WORK_COUNTERS);
+}
+
 // C[z] = A[z] * Bt[z]^T for z < Z. A: [Z][M][lda] int8, Bt: [Z][N][ldb] int8 (pitches in bytes, multiples of 16; plane
 // pitches pa, pb). fused = 0: C is int32 [Z][M][ldc]. fused = 1: C is int8 [Z][M][ldc] holding the balanced residue of
 // plane z mod modulus(first_modulus + z); ldc must then be a multiple of 16 with the padding columns writable.
@@ -696,6 +785,8 @@ cudaError_t gemm_i8_planes(const int8_t *A, const int8_t *Bt, void *C, int M, in
         const long long pairs_total = (long long)((M + g8::two::BM2 - 1) / g8::two::BM2) * p.tiles_n * Z;
         const int limit = mp[fused ? 1 : 0];
         const int pairs = (int)(pairs_total < limit ? pairs_total : limit);
+        if (!(p.counter = next_work_counter())) return cudaErrorInvalidDevice;
+        if ((e = cudaMemsetAsync(p.counter, 0, sizeof(int), st))) return e;
         if (fused) g8::gemm_i8_tc2<true><<<2 * pairs, g8::THREADS, g8::two::SMEM2_BYTES, st>>>(mapA, mapB, p);
         else g8::gemm_i8_tc2<false><<<2 * pairs, g8::THREADS, g8::two::SMEM2_BYTES, st>>>(mapA, mapB, p);
         return cudaGetLastError();

@@ -5,14 +5,16 @@ product admits without changing a single bit of the result: rank g owns a block 
 of C. Row scales are local to those rows; column scales and residues of B are recomputed identically on every rank, so
 the only exchange is one broadcast of B from the rank that holds it, on a communication stream. Two ways to cut it:
 
-* "rows": B travels in chunks of whole rows, straight out of the source's tensor (no packing). Each chunk only
+* "rows" (chosen when B is at most 1 GiB): B travels in chunks of whole rows, straight out of the source's tensor (no packing). Each chunk only
   feeds the running column maxima as it lands; the residues of B, the GEMMs and the reconstruction run once, over the
   full width, after the last chunk. Exposed cost: the broadcast minus the residues of A that run beside it.
-* "panels" (default): B travels in column panels (whole columns, packed panel-major on the source first), and each panel
+* "panels" (chosen for a larger B, in pieces of about 1 GiB): B travels in column panels (whole columns, packed panel-major on the source first), and each panel
   is scaled, multiplied and reconstructed as soon as it lands. More overlap, but narrower GEMM launches and a packing copy.
 
-Measured on two B200s at n = 8192, 16 moduli, 4 pieces: 8.41 ms per product with panels, 8.63 ms with rows (the transfer
-that rows leaves exposed costs more than the panels' narrower launches).
+Measured on two B200s, 16 moduli: at n = 8192 (B = 512 MiB) one row chunk 7.39 ms per product, two panels 7.75, four
+panels 7.86, against 7.03 on one GPU without any transfer; the single transfer leaves about 0.35 ms exposed, less than
+the panels' narrower launches cost. At n = 32768 (B = 8 GiB) the transfer would leave tens of milliseconds exposed, and
+panels hide all but the first.
 
 Peer memory is never read by a kernel of this library: B is in the GPU's own HBM before any kernel touches it.
 
@@ -32,6 +34,19 @@ def row_block(m_total, rank, world):
     base, extra = divmod(m_total, world)
     lo = rank * base + min(rank, extra)
     return lo, lo + base + (1 if rank < extra else 0)
+
+
+AUTO_PIECE_BYTES = 1 << 30
+
+
+def choose_layout(k, n, layout="auto", pieces=None):
+    """The broadcast layout and the number of pieces for a k x n FP64 B: what was asked for, else by the size of B."""
+    nbytes = 8 * k * n
+    if layout == "auto":
+        layout = "rows" if nbytes <= AUTO_PIECE_BYTES else "panels"
+    if pieces is None:
+        pieces = 1 if layout == "rows" else max(2, min(16, -(-nbytes // AUTO_PIECE_BYTES)))
+    return layout, pieces
 
 
 def row_chunks(k, chunks):
@@ -130,12 +145,13 @@ class RowShardedGemm:
 
     m_local, n, k: this rank's block of rows, the width of B/C and the inner length. `engine` defaults to the CUDA
     plan; tests on CPU ranks inject one with the same methods. `panels` is the number of pieces B is broadcast in
-    (row chunks for layout "rows", column panels for layout "panels").
+    (row chunks for layout "rows", column panels for layout "panels"); both default to a choice by the size of B.
     """
 
-    def __init__(self, m_local, n, k, moduli=16, group=None, src=0, panels=4, engine=None, device=None, layout="panels"):
-        if layout not in ("rows", "panels"):
-            raise ValueError("layout is 'rows' or 'panels'")
+    def __init__(self, m_local, n, k, moduli=16, group=None, src=0, panels=None, engine=None, device=None, layout="auto"):
+        if layout not in ("auto", "rows", "panels"):
+            raise ValueError("layout is 'auto', 'rows' or 'panels'")
+        layout, panels = choose_layout(k, n, layout, panels)
         self.group, self.src, self.layout = group, src, layout
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -148,10 +164,11 @@ class RowShardedGemm:
         if self.on_gpu:
             self.compute = torch.cuda.current_stream()
             self.comm = torch.cuda.Stream()
+            self.pack = torch.cuda.Stream()
             self._event = lambda: torch.cuda.Event()
         else:
             hs = _HostStreams()
-            self.compute, self.comm, self._event = hs.stream(), hs.stream(), hs.event
+            self.compute, self.comm, self.pack, self._event = hs.stream(), hs.stream(), hs.stream(), hs.event
         if self.world == 1:
             self.stage = None
         elif layout == "panels":   # panel-major staging: panel p is a contiguous k x width block, broadcast as one buffer
@@ -166,25 +183,42 @@ class RowShardedGemm:
             return c_local
         if self.layout == "rows":
             return self._by_rows(a_local, b, c_local)
+        # The source packs each panel (panel-major, contiguous) on a stream of its own, broadcasts it as soon as it is
+        # packed, and computes from its own B directly: its compute stream waits for nothing.
+        src = self.rank == self.src
+        start = self._event()
+        start.record(self.compute)                 # orders this call after the caller's writes of A and B
+        ctx = (lambda s: torch.cuda.stream(s)) if self.on_gpu else (lambda s: _null())
+        packed = []
+        if src:
+            self.pack.wait_event(start)
+            with ctx(self.pack):
+                for (lo, hi), buf in zip(self.ranges, self.stage):
+                    buf.copy_(b[:, lo:hi])
+                    ev = self._event()
+                    ev.record(self.pack)
+                    packed.append(ev)
         arrived = []
-        packed = self._event()
-        if self.rank == self.src:
-            for (lo, hi), buf in zip(self.ranges, self.stage):
-                buf.copy_(b[:, lo:hi])            # on the compute stream
-        packed.record(self.compute)
-        self.comm.wait_event(packed)
-        ctx = torch.cuda.stream(self.comm) if self.on_gpu else _null()
-        with ctx:
-            for buf in self.stage:
+        with ctx(self.comm):
+            for p, buf in enumerate(self.stage):
+                if src:
+                    self.comm.wait_event(packed[p])
                 dist.broadcast(buf, src=self.src, group=self.group)
                 ev = self._event()
                 ev.record(self.comm)
                 arrived.append(ev)
         self.engine.set_a(a_local, self.compute)   # overlaps the first panel's transfer
         for (lo, hi), buf, ev in zip(self.ranges, self.stage, arrived):
-            self.compute.wait_event(ev)
-            self.engine.panel(buf, c_local, lo, hi - lo, self.compute)
-        self.comm.wait_stream(self.compute)        # the staging buffers may be overwritten by the next call only after this one's reads
+            if src:
+                self.engine.panel(b[:, lo:hi], c_local, lo, hi - lo, self.compute)
+            else:
+                self.compute.wait_event(ev)
+                self.engine.panel(buf, c_local, lo, hi - lo, self.compute)
+        # the staging buffers may be overwritten by the next call only after this one's reads
+        self.comm.wait_stream(self.compute)
+        if src:
+            self.pack.wait_stream(self.comm)
+            self.compute.wait_stream(self.pack)    # the caller may overwrite B on the compute stream after this call
         return c_local
 
     def _by_rows(self, a_local, b, c_local):
@@ -208,11 +242,14 @@ class RowShardedGemm:
         self.engine.b_begin(self.compute)
         self.engine.set_a(a_local, self.compute)    # beside the transfer
         for (lo, hi), ev in zip(self.ranges, arrived):
-            self.compute.wait_event(ev)
+            if whole is self.stage:                 # a receiver, or a source that staged a strided B
+                self.compute.wait_event(ev)
             self.engine.b_rows(whole[lo:hi], self.compute)
         self.engine.b_finish(whole, self.compute)
         self.engine.multiply(c_local, self.compute)
         self.comm.wait_stream(self.compute)
+        if whole is b:
+            self.compute.wait_stream(self.comm)     # B was sent in place: the caller may overwrite it only after the sends
         return c_local
 
     def close(self):
