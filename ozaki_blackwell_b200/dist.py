@@ -40,13 +40,30 @@ AUTO_PIECE_BYTES = 1 << 30
 
 
 def choose_layout(k, n, layout="auto", pieces=None):
-    """The broadcast layout and the number of pieces for a k x n FP64 B: what was asked for, else by the size of B."""
+    """The broadcast layout and the number of pieces for a k x n FP64 B: what was asked for, else by the size of B.
+    pieces = 0 with layout "panels" means growing panels (see growing_panels)."""
     nbytes = 8 * k * n
     if layout == "auto":
         layout = "rows" if nbytes <= AUTO_PIECE_BYTES else "panels"
     if pieces is None:
-        pieces = 1 if layout == "rows" else max(2, min(16, -(-nbytes // AUTO_PIECE_BYTES)))
+        pieces = 1 if layout == "rows" else 0
     return layout, pieces
+
+
+def growing_panels(n):
+    """Column panels of n/16, 3n/16, n/4 and n/2 columns (starts on multiples of PANEL_ALIGN). The transfer of a panel
+    takes about a third of the time its product takes, so the first panel is small (its transfer hides behind the
+    residues of A, which need nothing of B), every later one has arrived before the one before it is used up, and most
+    of the columns sit in wide panels, whose GEMM launches run best."""
+    unit = max(PANEL_ALIGN, (n // 16) // PANEL_ALIGN * PANEL_ALIGN)
+    out, start = [], 0
+    for width in (unit, 3 * unit, 4 * unit):
+        if n - start <= width:
+            break
+        out.append((start, start + width))
+        start += width
+    out.append((start, n))
+    return out
 
 
 def row_chunks(k, chunks):
@@ -157,7 +174,10 @@ class RowShardedGemm:
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.m, self.n, self.k, self.moduli = m_local, n, k, moduli
         pieces = panels if self.world > 1 else 1
-        self.ranges = panel_ranges(n, pieces) if layout == "panels" else row_chunks(k, pieces)
+        if layout == "rows":
+            self.ranges = row_chunks(k, pieces)
+        else:
+            self.ranges = growing_panels(n) if pieces == 0 and self.world > 1 else panel_ranges(n, max(1, pieces))
         self.engine = engine if engine is not None else CudaEngine(m_local, n, k, moduli)
         self.on_gpu = engine is None or (device is not None and torch.device(device).type == "cuda")
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())

@@ -105,7 +105,12 @@ def test_partition_helpers():
         assert all(a[1] == b[0] for a, b in zip(blocks, blocks[1:]))
         assert max(h - l for l, h in blocks) - min(h - l for l, h in blocks) <= 1
     from ozaki_blackwell_b200.dist import choose_layout, row_chunks
-    assert choose_layout(8192, 8192) == ("rows", 1) and choose_layout(32768, 32768) == ("panels", 8)
+    from ozaki_blackwell_b200.dist import growing_panels
+    assert choose_layout(8192, 8192) == ("rows", 1) and choose_layout(32768, 32768) == ("panels", 0)
+    assert growing_panels(32768) == [(0, 2048), (2048, 8192), (8192, 16384), (16384, 32768)]
+    for n in (100, 256, 257, 1000, 5000, 12345):
+        r = growing_panels(n)
+        assert r[0][0] == 0 and r[-1][1] == n and all(a[1] == b[0] for a, b in zip(r, r[1:])) and all(lo % 256 == 0 for lo, _ in r)
     assert choose_layout(8192, 8192, "panels", 3) == ("panels", 3) and choose_layout(32768, 32768, "rows") == ("rows", 1)
     assert row_chunks(10, 3) == [(0, 4), (4, 7), (7, 10)] and row_chunks(2, 5) == [(0, 1), (1, 2)]
     for n, p in ((8192, 8), (8192, 1), (300, 4), (1000, 3), (256, 8), (32768, 16), (257, 2)):
