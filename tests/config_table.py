@@ -1,6 +1,6 @@
 """Prints the accuracy / speed table of the benchmark configurations on one GPU (a script, not a test):
 
-    python tests/config_table.py [--sizes 4096 8192] > gpurun_out/config_table.md
+    python tests/config_table.py [--sizes 4096 8192] > config_table.md
 
 For every size, modulus count (12, 14, 16 at n = 4096; 16 at the other sizes) and input family (U[-1,1) and U[-1,1) * 2^e,
 e in [-8, 8]): this library's time (median of 5 after a warm-up, CUDA events around the synchronous ozb_dgemm, as the
