@@ -13,8 +13,6 @@ cudaError_t scale_residues_cols(int nm, const double *X, int rows, int cols, lon
 cudaError_t cols_absmax_accumulate(const double *X, int rows, int cols, long long ldx, unsigned long long *colmax, cudaStream_t st);
 cudaError_t cols_residues_from_max(int nm, const double *X, int rows, int cols, long long ldx, int bits, const unsigned long long *colmax,
                                    int *s, int8_t *R, int ld, size_t plane, cudaStream_t st);
-cudaError_t scale_residues_rows_tc(int nm, const double *X, int rows, int len, long long ldx, int bits, int *s, int8_t *R, int ld,
-                                   size_t plane, int *status, cudaStream_t st);
 cudaError_t norm_scale_residues_rows(int nm, const double *X, int rows, int len, long long ldx, int beta, int *s, int8_t *R, int ld,
                                      size_t plane, cudaStream_t st);
 cudaError_t norm_scale_residues_cols(int nm, const double *X, int rows, int cols, long long ldx, int beta, int *s, int8_t *R, int ld,

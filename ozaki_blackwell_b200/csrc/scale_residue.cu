@@ -12,9 +12,7 @@
 // v + 2^62 = sum b_i 256^i with b_i unsigned, so v mod m = sum b_i (256^i mod m) - (2^62 mod m): two dp4a per modulus
 // and one multiply-high reduction of a 19-bit sum, instead of a 64-bit division by a constant.
 #include <mutex>
-#include <cstdlib>
 #include "oz_common.cuh"
-#include "oz_kernels.h"
 
 namespace ozk {
 
@@ -348,9 +346,6 @@ cudaError_t norm_scale_residues_cols(int nm, const double *X, int rows, int cols
 // A-like operand: `rows` rows of `len` contiguous doubles, row pitch ldx; writes s[rows] and R[nm][rows][ld]
 cudaError_t scale_residues_rows(int nm, const double *X, int rows, int len, long long ldx, int bits, int *s, int8_t *R, int ld,
                                 size_t plane, cudaStream_t st) {
-    static const bool use_tc = [] { const char *e = getenv("OZ_ROW_TC"); return e && *e == '1'; }();
-    if (use_tc && (ld & 3) == 0 && (plane & 3) == 0 && (reinterpret_cast<uintptr_t>(R) & 3) == 0)
-        return scale_residues_rows_tc(nm, X, rows, len, ldx, bits, s, R, ld, plane, nullptr, st);
     OZ_DISPATCH_NM(nm, (launch_rows_t<NM>(X, rows, len, ldx, bits, s, R, ld, plane, st)));
 }
 // The two passes of the B-like operand separately, for callers that receive the matrix in row chunks: the column maxima
