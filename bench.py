@@ -267,9 +267,9 @@ def run_ours(args):
             probe["cta_pair" if pair else "one_cta"] = best
         peak = max(probe.values())
         # DRAM bytes of one GEMM launch: the ncu capture at n = 4096 (profiles/gemm_i8_tc2_n4096_16moduli.md) measured
-        # 785.7 MB against 805.3 MB of algorithmic bytes (every residue byte read once, every product byte written once);
+        # 784.0 MB against 805.3 MB of algorithmic bytes (every residue byte read once, every product byte written once);
         # traffic is proportional to those bytes, so it is scaled to this launch by them
-        traffic = 785.7 / 805.3 * nm * (M * K + N * K + M * N)
+        traffic = 784.0 / 805.3 * nm * (M * K + N * K + M * N)
         roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": traffic,
                 "kernel": "gemm_i8_tc2<fused mod> (cta_group::2)", "peak_probe_int8_tops": probe,
                 "note": "INT8 tera-operations/s. peak = tensor-pipe probe measured in this run on this GPU (MEASURED_PEAKS.json holds "
