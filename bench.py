@@ -256,23 +256,32 @@ def run_ours(args):
         ops = 2.0 * nm * M * N * K
         achieved = ops / (phases[1] * 1e-3) / 1e12
         # the denominator: this GPU's own INT8 tensor rate, measured now by the library's probe (tcgen05.mma alone on
-        # random bytes, seconds-long so the power limit has settled), best of the one-CTA and the CTA-pair form
-        probe = {}
+        # random bytes, the GEMM kernel's instruction shape). Two figures, as for any kernel on a power-capped part: a burst
+        # of about a millisecond, and a run of about 0.1 s, after which the power limit has pulled the clock down. The GEMM
+        # kernel is timed inside steps that keep the GPU busy for far longer than that, so the sustained figure is its
+        # peak; the burst figure is reported beside it.
+        ms_p, tops_p = ctypes.c_float(), ctypes.c_double()
+        probe = {"burst_one_cta": 0.0, "burst_cta_pair": 0.0}
         for pair in (0, 1):
-            ms_p, tops_p = ctypes.c_float(), ctypes.c_double()
-            best = 0.0
             for _ in range(3):
-                check(lib.ozb_int8_peak(40000, pair, ctypes.byref(ms_p), ctypes.byref(tops_p)))
-                best = max(best, tops_p.value)
-            probe["cta_pair" if pair else "one_cta"] = best
-        peak = max(probe.values())
+                check(lib.ozb_int8_peak(2000, pair, ctypes.byref(ms_p), ctypes.byref(tops_p)))
+                key = "burst_cta_pair" if pair else "burst_one_cta"
+                probe[key] = max(probe[key], tops_p.value)
+        for _ in range(2):                      # the second run starts with the limit already active
+            check(lib.ozb_int8_peak(160000, 1, ctypes.byref(ms_p), ctypes.byref(tops_p)))
+        probe["sustained_cta_pair"] = tops_p.value
+        probe["sustained_ms"] = ms_p.value
+        peak = probe["sustained_cta_pair"]
+        burst = max(probe["burst_one_cta"], probe["burst_cta_pair"])
         # DRAM bytes of one GEMM launch: the ncu capture at n = 4096 (profiles/gemm_i8_tc2_n4096_16moduli.md) measured
         # 784.0 MB against 805.3 MB of algorithmic bytes (every residue byte read once, every product byte written once);
         # traffic is proportional to those bytes, so it is scaled to this launch by them
         traffic = 784.0 / 805.3 * nm * (M * K + N * K + M * N)
         roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": traffic,
-                "kernel": "gemm_i8_tc2<fused mod> (cta_group::2)", "peak_probe_int8_tops": probe,
-                "note": "INT8 tera-operations/s. peak = tensor-pipe probe measured in this run on this GPU (MEASURED_PEAKS.json holds "
+                "kernel": "gemm_i8_tc2<fused mod> (cta_group::2)", "peak_burst": burst, "frac_of_burst": achieved / burst,
+                "peak_probe_int8_tops": probe,
+                "note": "INT8 tera-operations/s. peak = sustained tensor-pipe probe (0.1 s of tcgen05.mma alone) measured in this run on "
+                "this GPU, the kernel being timed inside long steps; peak_burst = the same probe for 1 ms (MEASURED_PEAKS.json holds "
                 f"no INT8 figure); for comparison 2 x measured dense bf16: sustained {2 * pk['bf16']:.0f}, burst {2 * pk['bf16_burst']:.0f} "
                 f"({pk['source']}); nominal dense INT8 4500"}
 
