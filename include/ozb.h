@@ -93,6 +93,13 @@ int ozb_plan_b_begin(ozb_plan *p, void *stream);
 int ozb_plan_b_rows(ozb_plan *p, const double *Brows, long long ldb, int rows, void *stream);
 int ozb_plan_b_finish(ozb_plan *p, const double *B, long long ldb, void *stream);
 int ozb_plan_multiply(ozb_plan *p, double *C, long long ldc, void *stream);
+/* The same when the column maxima of B are known before B itself is complete (the holder of B computed them and sent
+ * them ahead): ozb_cols_absmax accumulates max |x| of every column of a row-major block into `colmax` (cols 64-bit words,
+ * the bit patterns of non-negative doubles; the caller clears them once), and ozb_plan_b_rows_residues forms the scales
+ * and the residues of rows [k0, k0 + rows) of B from such maxima as soon as those rows are there (k0 a multiple of 128).
+ * When all rows have been given, ozb_plan_multiply. */
+int ozb_cols_absmax(const double *X, int rows, int cols, long long ldx, void *colmax, void *stream);
+int ozb_plan_b_rows_residues(ozb_plan *p, const double *Brows, long long ldb, int k0, int rows, const void *colmax, void *stream);
 /* Workspace view, for stage-by-stage checks against the reference's Plan fields (src/ozaki2.cuh:117-119):
  * Ar [nm][M][Kp] int8, Br [nm][N][Kp] int8, Cr [nm][M][Np] int8 (balanced residues of the products, where the
  * reference keeps int32 Cl), sa [M], sb [N]. */

@@ -43,6 +43,8 @@ lib.ozb_plan_b_begin.argtypes = [_p, _p]
 lib.ozb_plan_b_rows.argtypes = [_p, _p, _ll, _i, _p]
 lib.ozb_plan_b_finish.argtypes = [_p, _p, _ll, _p]
 lib.ozb_plan_multiply.argtypes = [_p, _p, _ll, _p]
+lib.ozb_cols_absmax.argtypes = [_p, _i, _i, _ll, _p, _p]
+lib.ozb_plan_b_rows_residues.argtypes = [_p, _p, _ll, _i, _i, _p, _p]
 lib.ozb_plan_view.argtypes = [_p, _ip, _ip, _ip] + [ctypes.POINTER(_p)] * 5
 lib.ozb_plan_status.argtypes = [_p]
 lib.ozb_plan_profile.argtypes = [_p, _i]
@@ -66,7 +68,7 @@ lib.ozb_status.argtypes = []
 SYMBOLS = [
     "ozb_version", "ozb_error", "ozb_device", "ozb_dgemm", "ozb_ddgemm", "ozb_tdgemm", "ozb_release", "ozb_bench",
     "ozb_bits_for", "ozb_modulus", "ozb_plan_create", "ozb_plan_destroy", "ozb_plan_dgemm", "ozb_plan_set_a",
-    "ozb_plan_panel", "ozb_plan_b_begin", "ozb_plan_b_rows", "ozb_plan_b_finish", "ozb_plan_multiply", "ozb_plan_view", "ozb_plan_status", "ozb_plan_profile", "ozb_plan_phase_ms", "ozb_dgemm_ex", "ozb_dgemm_norm", "ozb_ddgemm_ex", "ozb_bf16_fp8_gemm",
+    "ozb_plan_panel", "ozb_plan_b_begin", "ozb_plan_b_rows", "ozb_plan_b_finish", "ozb_plan_multiply", "ozb_cols_absmax", "ozb_plan_b_rows_residues", "ozb_plan_view", "ozb_plan_status", "ozb_plan_profile", "ozb_plan_phase_ms", "ozb_dgemm_ex", "ozb_dgemm_norm", "ozb_ddgemm_ex", "ozb_bf16_fp8_gemm",
     "ozb_scale_residues_rows", "ozb_scale_residues_cols", "ozb_scale_residues_cols_static", "ozb_gemm_i8", "ozb_gemm_i8_mod", "ozb_crt_i32", "ozb_crt_i8",
     "ozb_status", "ozb_int8_peak", "ozb_selftest_wait_expiry",
 ]

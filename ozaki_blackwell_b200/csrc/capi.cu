@@ -601,6 +601,19 @@ OZB_API int ozb_plan_b_finish(ozb_plan *p, const double *B, long long ldb, void 
     std::lock_guard<std::mutex> g(mu);
     return (int)cols_residues_from_max(p->nm, B, p->K, p->N, ldb, p->bits, p->colmax, p->sb, p->Br, p->Kp, p->planeB, (cudaStream_t)stream);
 }
+// rows [k0, k0 + rows) of B with column maxima the caller holds (computed where the whole of B is, e.g. on another GPU)
+OZB_API int ozb_plan_b_rows_residues(ozb_plan *p, const double *Brows, long long ldb, int k0, int rows, const void *colmax, void *stream) {
+    if (!p || !Brows || !colmax || rows <= 0 || k0 < 0 || (k0 & 127) || k0 + rows > p->K || ldb < p->N) return OZB_EARG;
+    std::lock_guard<std::mutex> g(mu);
+    p->last = (cudaStream_t)stream;
+    return (int)cols_residues_from_max(p->nm, Brows, rows, p->N, ldb, p->bits, (const unsigned long long *)colmax, p->sb, p->Br + k0, p->Kp,
+                                       p->planeB, (cudaStream_t)stream);
+}
+OZB_API int ozb_cols_absmax(const double *X, int rows, int cols, long long ldx, void *colmax, void *stream) {
+    if (int e = check_args(rows, cols, 1)) return e;
+    if (!X || !colmax || ldx < cols) return OZB_EARG;
+    return (int)cols_absmax_accumulate(X, rows, cols, ldx, (unsigned long long *)colmax, (cudaStream_t)stream);
+}
 OZB_API int ozb_plan_multiply(ozb_plan *p, double *C, long long ldc, void *stream) {
     if (!p || !C || ldc < p->N) return OZB_EARG;
     std::lock_guard<std::mutex> g(mu);

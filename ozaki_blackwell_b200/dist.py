@@ -5,15 +5,18 @@ product admits without changing a single bit of the result: rank g owns a block 
 of C. Row scales are local to those rows; column scales and residues of B are recomputed identically on every rank, so
 the only exchange is one broadcast of B from the rank that holds it, on a communication stream. Two ways to cut it:
 
-* "rows" (chosen when B is at most 1 GiB): B travels in chunks of whole rows, straight out of the source's tensor (no packing). Each chunk only
-  feeds the running column maxima as it lands; the residues of B, the GEMMs and the reconstruction run once, over the
-  full width, after the last chunk. Exposed cost: the broadcast minus the residues of A that run beside it.
+* "rows" (chosen when B is at most 1 GiB): B travels as whole rows, straight out of the source's tensor (no packing),
+  and the GEMMs and the reconstruction run once, over the full width. In one piece, the exposed cost is the broadcast
+  minus the residues of A that run beside it. In several pieces, the source first reduces the column maxima of its B and
+  sends those 8 n bytes ahead, so that every receiver turns each chunk of rows into residues the moment it lands.
 * "panels" (chosen for a larger B, in pieces of about 1 GiB): B travels in column panels (whole columns, packed panel-major on the source first), and each panel
   is scaled, multiplied and reconstructed as soon as it lands. More overlap, but narrower GEMM launches and a packing copy.
 
 Measured on two B200s, 16 moduli: at n = 8192 (B = 512 MiB) one row chunk 7.39 ms per product, two panels 7.75, four
 panels 7.86, against 7.03 on one GPU without any transfer; the single transfer leaves about 0.35 ms exposed, less than
-the panels' narrower launches cost. At n = 32768 (B = 8 GiB) the transfer would leave tens of milliseconds exposed, and
+the panels' narrower launches cost. Row chunks with the maxima sent ahead do not beat the single piece either: 8.02 ms with
+two chunks, 7.39 when the communication stream is given high priority (a transfer kernel launched while another kernel's
+blocks are still being dispatched otherwise waits for them), which is what one piece takes without it. At n = 32768 (B = 8 GiB) the transfer would leave tens of milliseconds exposed, and
 panels hide all but the first.
 
 Peer memory is never read by a kernel of this library: B is in the GPU's own HBM before any kernel touches it.
@@ -66,10 +69,20 @@ def growing_panels(n):
     return out
 
 
+ROW_ALIGN = 128   # ozb_plan_b_rows_residues wants chunk starts on multiples of 128 rows
+
+
 def row_chunks(k, chunks):
-    """Split k rows into at most `chunks` contiguous ranges of near-equal length."""
-    chunks = max(1, min(chunks, k))
-    return [row_block(k, c, chunks) for c in range(chunks)]
+    """Split k rows into at most `chunks` contiguous ranges of near-equal length whose starts are multiples of ROW_ALIGN."""
+    blocks = (k + ROW_ALIGN - 1) // ROW_ALIGN
+    chunks = max(1, min(chunks, blocks))
+    out, start = [], 0
+    for c in range(chunks):
+        nb = blocks // chunks + (1 if c < blocks % chunks else 0)
+        stop = min(k, start + nb * ROW_ALIGN)
+        out.append((start, stop))
+        start = stop
+    return out
 
 
 def panel_ranges(n, panels):
@@ -114,6 +127,13 @@ class CudaEngine:
 
     def b_rows(self, rows, stream):
         self._check(self._lib.ozb_plan_b_rows(self._plan, rows.data_ptr(), rows.stride(0), rows.shape[0], stream.cuda_stream))
+
+    def cols_absmax(self, b, colmax, stream):
+        self._check(self._lib.ozb_cols_absmax(b.data_ptr(), b.shape[0], b.shape[1], b.stride(0), colmax.data_ptr(), stream.cuda_stream))
+
+    def b_rows_residues(self, rows, k0, colmax, stream):
+        self._check(self._lib.ozb_plan_b_rows_residues(self._plan, rows.data_ptr(), rows.stride(0), k0, rows.shape[0], colmax.data_ptr(),
+                                                       stream.cuda_stream))
 
     def b_finish(self, b, stream):
         self._check(self._lib.ozb_plan_b_finish(self._plan, b.data_ptr(), b.stride(0), stream.cuda_stream))
@@ -195,6 +215,7 @@ class RowShardedGemm:
             self.stage = [torch.empty((k, hi - lo), dtype=torch.float64, device=self.device) for lo, hi in self.ranges]
         else:                      # the receivers' copy of B (the source sends from its own tensor when that is contiguous)
             self.stage = torch.empty((k, n), dtype=torch.float64, device=self.device)
+            self.colmax = torch.zeros(n, dtype=torch.int64, device=self.device)   # bit patterns of the column maxima of |B|
 
     def __call__(self, a_local, b, c_local):
         """a_local [m_local, k], c_local [m_local, n]; b [k, n] is read on rank `src` only (others may pass None)."""
@@ -242,6 +263,8 @@ class RowShardedGemm:
         return c_local
 
     def _by_rows(self, a_local, b, c_local):
+        if len(self.ranges) > 1:
+            return self._by_rows_maxima_first(a_local, b, c_local)
         if self.rank == self.src and b.is_contiguous():
             whole = b                               # sent in place, nothing staged
         else:
@@ -251,25 +274,57 @@ class RowShardedGemm:
         ready = self._event()
         ready.record(self.compute)                  # orders the copy above, and the previous call's reads of the stage
         self.comm.wait_event(ready)
-        arrived = []
         ctx = torch.cuda.stream(self.comm) if self.on_gpu else _null()
         with ctx:
-            for lo, hi in self.ranges:
-                dist.broadcast(whole[lo:hi], src=self.src, group=self.group)
-                ev = self._event()
-                ev.record(self.comm)
-                arrived.append(ev)
+            dist.broadcast(whole, src=self.src, group=self.group)
+            arrived = self._event()
+            arrived.record(self.comm)
         self.engine.b_begin(self.compute)
         self.engine.set_a(a_local, self.compute)    # beside the transfer
-        for (lo, hi), ev in zip(self.ranges, arrived):
-            if whole is self.stage:                 # a receiver, or a source that staged a strided B
-                self.compute.wait_event(ev)
-            self.engine.b_rows(whole[lo:hi], self.compute)
+        if whole is self.stage:                     # a receiver, or a source that staged a strided B
+            self.compute.wait_event(arrived)
+        self.engine.b_rows(whole, self.compute)
         self.engine.b_finish(whole, self.compute)
         self.engine.multiply(c_local, self.compute)
         self.comm.wait_stream(self.compute)
         if whole is b:
             self.compute.wait_stream(self.comm)     # B was sent in place: the caller may overwrite it only after the sends
+        return c_local
+
+    def _by_rows_maxima_first(self, a_local, b, c_local):
+        """Several row chunks: the source first reduces the column maxima of its B (one pass) and sends those 8 n bytes
+        ahead, so that every receiver can turn each chunk of rows into residues the moment it lands."""
+        src = self.rank == self.src
+        in_place = src and b.is_contiguous()
+        whole = b if in_place else self.stage
+        if src:
+            if not in_place:
+                whole.copy_(b)
+            self.colmax.zero_()
+            self.engine.cols_absmax(whole, self.colmax, self.compute)
+        ready = self._event()
+        ready.record(self.compute)
+        self.comm.wait_event(ready)
+        arrived = []
+        ctx = torch.cuda.stream(self.comm) if self.on_gpu else _null()
+        with ctx:
+            dist.broadcast(self.colmax, src=self.src, group=self.group)
+            for lo, hi in self.ranges:
+                dist.broadcast(whole[lo:hi], src=self.src, group=self.group)
+                ev = self._event()
+                ev.record(self.comm)
+                arrived.append(ev)
+        self.engine.set_a(a_local, self.compute)    # beside the transfer
+        if src:
+            self.engine.b_rows_residues(whole, 0, self.colmax, self.compute)
+        else:
+            for (lo, hi), ev in zip(self.ranges, arrived):
+                self.compute.wait_event(ev)         # the maxima were sent before the first chunk on the same stream
+                self.engine.b_rows_residues(whole[lo:hi], lo, self.colmax, self.compute)
+        self.engine.multiply(c_local, self.compute)
+        self.comm.wait_stream(self.compute)
+        if in_place:
+            self.compute.wait_stream(self.comm)
         return c_local
 
     def close(self):

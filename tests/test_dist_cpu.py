@@ -22,8 +22,8 @@ sys.path.insert(0, os.path.dirname(HERE))
 class CheckerEngine:
     """set_a / panel / full of the CUDA engine, answered by the CPU checker on torch CPU tensors."""
 
-    def __init__(self, nm):
-        self.nm, self.A, self.calls = nm, None, []
+    def __init__(self, nm, k=None):
+        self.nm, self.A, self.calls, self.k = nm, None, [], k
 
     def set_a(self, a, stream):
         self.A = a.numpy().copy()
@@ -38,6 +38,20 @@ class CheckerEngine:
 
     def b_rows(self, rows, stream):
         self.rows.append(rows.numpy().copy())
+
+    def cols_absmax(self, b, colmax, stream):
+        m = np.abs(b.numpy()).max(axis=0)
+        colmax.copy_(torch.from_numpy(np.maximum(m.view(np.int64), colmax.numpy())))
+
+    def b_rows_residues(self, rows, k0, colmax, stream):
+        if k0 == 0:
+            self.rows, self.maxima = [], colmax.numpy().copy()
+        assert k0 == sum(r.shape[0] for r in self.rows) and k0 % 128 == 0
+        self.rows.append(rows.numpy().copy())
+        self.B = np.vstack(self.rows)
+        if self.B.shape[0] == self.k:               # complete: the maxima sent ahead are those of the whole of B
+            assert np.array_equal(self.maxima, np.abs(self.B).max(axis=0).view(np.int64))
+            self.calls.append((len(self.rows), self.k))
 
     def b_finish(self, b, stream):
         self.B = b.numpy().copy()
@@ -64,7 +78,7 @@ def _worker(rank, world, port, M, N, K, nm, panels, src, layout, out_dir):
     a_local = torch.from_numpy(A[lo:hi].copy())
     b = torch.from_numpy(B.copy()) if rank == src else None     # only the source rank holds B
     c_local = torch.zeros((hi - lo, N), dtype=torch.float64)
-    eng = CheckerEngine(nm)
+    eng = CheckerEngine(nm, K)
     op = RowShardedGemm(hi - lo, N, K, nm, src=src, panels=panels, engine=eng, device="cpu", layout=layout)
     op(a_local, b, c_local)
     op(a_local, b, c_local)                                     # a second call reuses the staging buffers
@@ -79,7 +93,7 @@ def _worker(rank, world, port, M, N, K, nm, panels, src, layout, out_dir):
 def test_two_ranks_match_the_unsharded_product(tmp_path, src, layout):
     import oracle_lib as o
     from ozaki_blackwell_b200.dist import panel_ranges, row_block
-    M, N, K, nm, panels, world = 37, 600, 96, 16, 3, 2
+    M, N, K, nm, panels, world = 37, 600, 300, 16, 3, 2
     port = 29500 + (os.getpid() % 2000) + src + 2 * (layout == "rows")
     mp.spawn(_worker, args=(world, port, M, N, K, nm, panels, src, layout, str(tmp_path)), nprocs=world, join=True)
     rng = np.random.default_rng(123)
@@ -93,7 +107,7 @@ def test_two_ranks_match_the_unsharded_product(tmp_path, src, layout):
         if layout == "panels":
             assert calls == [(lo, hi - lo) for lo, hi in panel_ranges(N, panels)] * 2
         else:
-            assert calls == [(panels, K)] * 2
+            assert calls == [(1 if r == src else panels, K)] * 2   # the source turns its own B into residues in one go
     assert row_block(M, 0, world) == (0, 19) and row_block(M, 1, world) == (19, 37)
 
 
@@ -112,7 +126,7 @@ def test_partition_helpers():
         r = growing_panels(n)
         assert r[0][0] == 0 and r[-1][1] == n and all(a[1] == b[0] for a, b in zip(r, r[1:])) and all(lo % 256 == 0 for lo, _ in r)
     assert choose_layout(8192, 8192, "panels", 3) == ("panels", 3) and choose_layout(32768, 32768, "rows") == ("rows", 1)
-    assert row_chunks(10, 3) == [(0, 4), (4, 7), (7, 10)] and row_chunks(2, 5) == [(0, 1), (1, 2)]
+    assert row_chunks(1000, 3) == [(0, 384), (384, 768), (768, 1000)] and row_chunks(100, 5) == [(0, 100)]
     for n, p in ((8192, 8), (8192, 1), (300, 4), (1000, 3), (256, 8), (32768, 16), (257, 2)):
         r = panel_ranges(n, p)
         assert r[0][0] == 0 and r[-1][1] == n and len(r) <= max(p, 1)

@@ -68,6 +68,17 @@ def test_plan_interface_with_leading_dimensions_and_a_stream():
     g.check(lib.ozb_plan_status(plan))
     assert g.same_bits(Cd[:, :N].cpu().numpy(), o.dgemm(A2, B, nm))
     assert lib.ozb_plan_b_rows(plan, g.ptr(Bd), ldb, K + 1, None) == 10001
+    # the column maxima first (as their holder would send them ahead), then B in chunks of rows starting on multiples of 128
+    Cd.fill_(0)
+    colmax = torch.zeros(N, dtype=torch.int64, device="cuda")
+    g.check(lib.ozb_cols_absmax(g.ptr(Bd), K, N, ldb, g.ptr(colmax), None))
+    assert np.array_equal(colmax.cpu().numpy(), np.abs(B).max(axis=0).view(np.int64))
+    for k0, rows in ((256, K - 256), (0, 128), (128, 128)):
+        g.check(lib.ozb_plan_b_rows_residues(plan, ctypes.c_void_p(Bd.data_ptr() + 8 * ldb * k0), ldb, k0, rows, g.ptr(colmax), None))
+    g.check(lib.ozb_plan_multiply(plan, g.ptr(Cd), ldc, None))
+    g.check(lib.ozb_plan_status(plan))
+    assert g.same_bits(Cd[:, :N].cpu().numpy(), o.dgemm(A2, B, nm))
+    assert lib.ozb_plan_b_rows_residues(plan, g.ptr(Bd), ldb, 100, 28, g.ptr(colmax), None) == 10001
     lib.ozb_plan_destroy(plan)
 
 
