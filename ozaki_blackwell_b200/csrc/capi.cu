@@ -108,7 +108,6 @@ static int plan_make(int M, int N, int K, int nm, int maxbits, ozb_plan **out) {
     cudaGetDevice(&p->dev);
     p->bits = bits_for_impl(nm, K, maxbits);
     p->Kp = round_up(K, 128);   // rows start on 128-byte lines; the TMA extent is K itself, so the padding is never read
-    { const char *env = getenv("OZ_KPAD"); if (env && *env) p->Kp += atoi(env) / 128 * 128; }   // experiment: break power-of-two pitches
     p->Np = round_up(N, 16);
     p->planeA = (size_t)M * p->Kp; p->planeB = (size_t)N * p->Kp; p->planeC = (size_t)M * p->Np;
     cudaError_t e = cudaMalloc(&p->Ar, nm * p->planeA);
