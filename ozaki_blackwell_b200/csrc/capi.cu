@@ -275,10 +275,15 @@ static int plan_dgemm_host(ozb_plan *p, const double *A, const double *B, double
         if (!e) e = cols_absmax_accumulate(p->hB + k0 * N, rows, (int)N, (long long)N, p->colmax, p->sRun);
     }
     if (!e) e = cols_residues_from_max(p->nm, p->hB, (int)K, (int)N, (long long)N, p->bits, p->colmax, p->sb, p->Br, p->Kp, p->planeB, p->sRun);
-    for (int q = 0; q < blocks && !e; q++) {   // A, block of rows by block; C goes back block by block
-        const size_t i0 = (size_t)q * mblock;
-        if (i0 >= M) break;
-        const int m = (int)(M - i0 < (size_t)mblock ? M - i0 : mblock);
+    // A, block of rows by block; C goes back block by block. What remains after the last block has landed (its residues,
+    // GEMMs, reconstruction and the copy of its rows of C) is exposed, so the last blocks are small: the final mblock rows
+    // go as halves of halves down to 128 rows.
+    size_t i0 = 0;
+    for (int q = 0; i0 < M && !e; q++) {
+        const size_t left = M - i0;
+        size_t m_ = left > (size_t)mblock ? (size_t)mblock : (left > 128 ? (left / 2 + 127) / 128 * 128 : left);
+        if (q >= HOST_PANELS - 1 || m_ > left) m_ = left;   // the event arrays are finite
+        const int m = (int)m_;
         e = cudaMemcpyAsync(p->hA + i0 * K, A + i0 * K, (size_t)m * K * 8, cudaMemcpyHostToDevice, p->sIn);
         if (!e) e = cudaEventRecord(p->evIn[q], p->sIn);
         if (!e) e = cudaStreamWaitEvent(p->sRun, p->evIn[q], 0);
@@ -288,6 +293,7 @@ static int plan_dgemm_host(ozb_plan *p, const double *A, const double *B, double
         if (!e) e = cudaEventRecord(p->evRun[q], p->sRun);
         if (!e) e = cudaStreamWaitEvent(p->sOut, p->evRun[q], 0);
         if (!e) e = cudaMemcpyAsync(C + i0 * N, p->hC + i0 * N, (size_t)m * N * 8, cudaMemcpyDeviceToHost, p->sOut);
+        i0 += m_;
     }
     if (!e) e = cudaStreamSynchronize(p->sOut);
     cudaError_t e2 = cudaStreamSynchronize(p->sRun), e3 = cudaStreamSynchronize(p->sIn);
