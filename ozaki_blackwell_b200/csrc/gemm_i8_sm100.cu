@@ -442,7 +442,14 @@ gemm_i8_tc2(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
         asm volatile("ld.shared.b32 %0, [%1];" : "=r"(w) : "r"(work_ring + 4u * s) : "memory");
         return w;
     };
-    auto work_taken = [&](uint32_t n) { mbar_arrive_cluster(map_to_cta(taken_bar(n % WORK_SLOTS), 1)); };
+    // "this role has read slot n": a plain remote arrive whose address depends on the value read (w >= -1 always, which
+    // the compiler cannot know), so it cannot be issued before the load has returned. The scheduler refills the slot only
+    // after all eleven arrivals and an atomic round trip; a cluster-scope release on every arrive would stall the issuer
+    // for about a microsecond per tile.
+    auto work_taken = [&](uint32_t n, int w) {
+        const uint32_t never = w < -1 ? 8u : 0u;
+        mbar_arrive_cluster(map_to_cta(taken_bar(n % WORK_SLOTS) + never, 1));
+    };
 #ifdef OZ_TIMING
     long long t_wait = 0, t_all = clock64();
 #define OZ_T0 const long long t0_ = clock64();
@@ -457,7 +464,7 @@ gemm_i8_tc2(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
             uint32_t it = 0;
             for (uint32_t n = 0; !*abortp; n++) {
                 const int w = next_work(n, 0x60 + (int)rank);
-                work_taken(n);
+                work_taken(n, w);
                 if (w < 0) break;
                 int z, tm, tn;
                 decode_work(pp, w, z, tm, tn);
@@ -482,7 +489,7 @@ gemm_i8_tc2(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
             uint32_t it = 0;
             for (uint32_t n = 0; !*abortp; n++) {
                 const int w = next_work(n, 0x62);
-                work_taken(n);
+                work_taken(n, w);
                 if (w < 0) break;
                 const uint32_t acc = n & 1u;
                 if (!mbar_wait(accempty_bar(acc), ((n >> 1) & 1u) ^ 1u, abortp, 0x20 + ((int)(n & 0xfff) << 8))) break;
@@ -526,7 +533,7 @@ gemm_i8_tc2(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
         for (uint32_t n = 0; !*abortp; n++) {
             const int w = next_work(n, 0x64 + (int)rank);
             __syncwarp();
-            if (lane == 0) work_taken(n);
+            if (lane == 0) work_taken(n, w);
             if (__any_sync(~0u, w < 0)) break;
             int z, tm, tn;
             decode_work(pp, w, z, tm, tn);
