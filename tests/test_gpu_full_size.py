@@ -77,3 +77,46 @@ def test_full_size_properties(n, nm):
     if nm == 16:
         idx = np.random.default_rng(2).integers(0, got.size, 512)
         assert o.err_units_sampled(Ah, Bh, got, idx) <= 2.0     # the target at n = 8192, 16 moduli
+
+
+def test_double_double_at_n4096():
+    """Configuration 3: hi = U[-1,1) 2^e, lo = hi U[-1,1) 2^-53, n = 4096, 32 moduli. Powers of two move into the scales
+    (hi and lo parts both), a block of rows alone gives the same rows, a band of rows equals the checker's, and a 64 x 64
+    sample stays within the reference's published error against the quad-precision product."""
+    import torch
+    import gpu_util as g
+    from ozaki_blackwell_b200._lib import lib
+    n = 4096
+    Ah, Bh = _device_inputs(n, 301), _device_inputs(n, 302)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(303)
+    Al = Ah * 2.0 ** -53 * (torch.rand((n, n), generator=gen, dtype=torch.float64, device="cuda") * 2 - 1)
+    Bl = Bh * 2.0 ** -53 * (torch.rand((n, n), generator=gen, dtype=torch.float64, device="cuda") * 2 - 1)
+
+    def dd(ah, al, bh, bl):
+        m, k = ah.shape
+        ch = torch.full((m, bh.shape[1]), float("nan"), dtype=torch.float64, device="cuda")
+        cl = torch.full_like(ch, float("nan"))
+        ops = [x.contiguous() for x in (ah, al, bh, bl)]
+        torch.cuda.synchronize()
+        g.check(lib.ozb_ddgemm(m, bh.shape[1], k, *[g.ptr(x) for x in ops], g.ptr(ch), g.ptr(cl), 0))
+        return ch, cl
+
+    Ch, Cl = dd(Ah, Al, Bh, Bl)
+    assert bool(torch.isfinite(Ch).all()) and bool(torch.isfinite(Cl).all())
+    Ch2, Cl2 = dd(Ah * 2.0 ** 5, Al * 2.0 ** 5, Bh * 2.0 ** -9, Bl * 2.0 ** -9)
+    assert _same(Ch2, Ch * 2.0 ** -4) and _same(Cl2, Cl * 2.0 ** -4)
+    lo, hi = 1234, 1234 + 333
+    Ch3, Cl3 = dd(Ah[lo:hi], Al[lo:hi], Bh, Bl)
+    assert _same(Ch3, Ch[lo:hi]) and _same(Cl3, Cl[lo:hi])
+    rows = slice(2000, 2004)
+    host = [x.cpu().numpy() for x in (Ah[rows], Al[rows], Bh, Bl)]
+    Wh, Wl = o.ddgemm(*host, 32)
+    assert np.array_equal(Ch[rows].cpu().numpy().view(np.uint64), Wh.view(np.uint64))
+    assert np.array_equal(Cl[rows].cpu().numpy().view(np.uint64), Wl.view(np.uint64))
+    # 64 x 64 sample against the quad-precision product (bench/dd_test.cu measures the same; it publishes 12.6 units of
+    # 2^-106 at K = 1024 for this input family, and the error grows slowly with K)
+    r, c = slice(512, 576), slice(3000, 3064)
+    sub = [Ah[r].cpu().numpy(), Al[r].cpu().numpy(), Bh[:, c].cpu().numpy(), Bl[:, c].cpu().numpy()]
+    err = o.dd_err_units(Ch[r, c].cpu().numpy(), Cl[r, c].cpu().numpy(), *o.ref_quad(*sub))
+    assert err <= 64.0, err
