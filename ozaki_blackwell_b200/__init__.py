@@ -1,16 +1,20 @@
-"""FP64-accurate matrix products from the INT8 tensor cores of NVIDIA B200 (sm_100a): Ozaki scheme II.
+"""FP64-accurate matrix products on NVIDIA B200 (sm_100a) from exact INT8 tensor-core products: Ozaki scheme II.
 
-The interface is the reference package's (python/ozaki_blackwell/__init__.py of ShabanEjupi/ozaki-blackwell):
+Public names and their meaning follow the reference's Python package (python/ozaki_blackwell/__init__.py of
+ShabanEjupi/ozaki-blackwell), so that code written against it runs unchanged:
 
-    import numpy as np, ozaki_blackwell_b200 as ob
-    C = ob.matmul(A, B)              # float64, NumPy arrays in and out (staged through the GPU)
-    C = ob.matmul(At, Bt)            # CUDA arrays (torch tensors, anything with __cuda_array_interface__) stay on the GPU
+    matmul(a, b, moduli=16, out=None)     C = A B, float64 row-major; 8 <= moduli <= 16
+    matmul_dd((ah, al), (bh, bl))         double-double product, returns (Ch, Cl)
+    matmul_td(...)                        triple-double: part of the interface, not built here (raises OzakiError)
+    device(), release(), bench(n, kind, reps), OzakiError
 
-Arrays are float64 and row-major; `moduli` (8..16) trades accuracy for speed exactly as in the reference, and the result
-is bit-identical to the reference's for the same inputs and modulus count. Everything is computed by
-libozaki_blackwell.so on the GPU; there is no CPU path.
+Operands are either all host arrays (anything numpy can view as float64; the library stages them through the GPU) or all
+device arrays exposing __cuda_array_interface__ (torch, cupy, numba, ...; nothing leaves the GPU). Results are bit-identical
+to the reference's for the same inputs and modulus count. All arithmetic happens in libozaki_blackwell.so on the GPU: a
+missing library is an ImportError, a GPU that is not compute capability 10.x an OzakiError.
 """
 import ctypes
+import importlib
 
 import numpy as np
 
@@ -21,119 +25,156 @@ __all__ = ["matmul", "matmul_dd", "matmul_td", "device", "release", "bench", "Oz
 
 
 class OzakiError(RuntimeError):
-    pass
+    """A non-zero status of the C library, with the library's own text for it."""
+
+    def __init__(self, code):
+        self.code = int(code)
+        super().__init__(_lib.ozb_error(self.code).decode())
 
 
-def _check(code):
-    if code:
-        raise OzakiError(_lib.ozb_error(code).decode())
+class _DeviceSide:
+    """How to treat operands that live on the GPU: pointer extraction, stream hand-over, allocation of results."""
+
+    @staticmethod
+    def owns(x):
+        return hasattr(x, "__cuda_array_interface__")
+
+    @staticmethod
+    def describe(x, role):
+        iface = x.__cuda_array_interface__
+        shape, strides = tuple(iface["shape"]), iface.get("strides")
+        if iface["typestr"] != "<f8" or len(shape) != 2:
+            raise TypeError(f"{role} must be a two-dimensional float64 device array (typestr {iface['typestr']}, shape {shape})")
+        if strides is not None and tuple(strides) != (8 * shape[1], 8):
+            raise TypeError(f"{role} must be row-major and dense; make it contiguous first")
+        return shape, int(iface["data"][0])
+
+    @staticmethod
+    def hand_over(x):
+        # the library launches on the legacy default stream: whatever the framework queued on its own stream must be done
+        family = type(x).__module__.partition(".")[0]
+        if family == "torch":
+            importlib.import_module("torch").cuda.current_stream(x.device).synchronize()
+        elif family == "cupy":
+            importlib.import_module("cupy").cuda.get_current_stream().synchronize()
+
+    @staticmethod
+    def result_like(x, shape):
+        family = type(x).__module__.partition(".")[0]
+        if family == "torch":
+            return x.new_empty(shape)
+        if family == "cupy":
+            return importlib.import_module("cupy").empty(shape, dtype="float64")
+        raise TypeError(f"cannot allocate a result for {type(x).__name__}: give out=")
+
+    on_host_flag = 0
 
 
-def _is_cuda(x):
-    return hasattr(x, "__cuda_array_interface__")
+class _HostSide:
+    """Operands in host memory: made contiguous float64 once, results as numpy arrays."""
+
+    @staticmethod
+    def owns(x):
+        return not _DeviceSide.owns(x)
+
+    @staticmethod
+    def describe(x, role):
+        if x.ndim != 2:
+            raise ValueError(f"{role} must be two-dimensional, got {x.ndim} dimensions")
+        return x.shape, x.ctypes.data
+
+    @staticmethod
+    def hand_over(x):
+        pass
+
+    @staticmethod
+    def result_like(x, shape):
+        return np.empty(shape, dtype=np.float64)
+
+    on_host_flag = 1
 
 
-def _cuda_ptr(x, what):
-    ai = x.__cuda_array_interface__
-    if ai["typestr"] != "<f8" or len(ai["shape"]) != 2:
-        raise TypeError(f"{what}: a 2-D float64 CUDA array is needed, got {ai['typestr']} with shape {ai['shape']}")
-    if ai.get("strides") not in (None, (ai["shape"][1] * 8, 8)):
-        raise TypeError(f"{what}: the CUDA array must be C-contiguous (call .contiguous())")
-    return ai["data"][0], tuple(ai["shape"])
-
-
-def _sync(x):
-    """Wait for the stream that produced x: the products run on the legacy default stream, as in the reference."""
-    mod = type(x).__module__.split(".")[0]
-    if mod == "torch":
-        import torch
-        torch.cuda.current_stream(x.device).synchronize()
-    elif mod == "cupy":
-        import cupy
-        cupy.cuda.get_current_stream().synchronize()
-
-
-def _empty_like_cuda(x, shape):
-    mod = type(x).__module__.split(".")[0]
-    if mod == "torch":
-        return x.new_empty(shape)
-    if mod == "cupy":
-        import cupy
-        return cupy.empty(shape, dtype=cupy.float64)
-    raise TypeError("for this CUDA array type pass out= (C-contiguous float64 arrays of the result's shape)")
-
-
-def _shapes(a_parts, b_parts):
-    (m, k), (k2, n) = a_parts[0].shape, b_parts[0].shape
-    if k != k2:
-        raise ValueError(f"inner dimensions differ: {a_parts[0].shape} @ {b_parts[0].shape}")
-    if any(x.shape != (m, k) for x in a_parts):
-        raise ValueError("all parts of A must have one shape")
-    if any(x.shape != (k, n) for x in b_parts):
-        raise ValueError("all parts of B must have one shape")
-    return m, n, k
-
-
-def _run(fn, a_parts, b_parts, nout, extra, out):
-    if any(_is_cuda(x) for x in a_parts + b_parts):
-        if not all(_is_cuda(x) for x in a_parts + b_parts):
-            raise TypeError("mix of CUDA and host arrays: move all of them to one side")
-        ptrs, shapes = zip(*(_cuda_ptr(x, "input") for x in a_parts + b_parts))
-        m, k = shapes[0]
-        n = shapes[len(a_parts)][1]
-        if any(s != (m, k) for s in shapes[:len(a_parts)]) or any(s != (k, n) for s in shapes[len(a_parts):]):
-            raise ValueError(f"shapes do not match: {shapes}")
-        outs = list(out) if out is not None else [_empty_like_cuda(a_parts[0], (m, n)) for _ in range(nout)]
-        optr = [_cuda_ptr(o, "out")[0] for o in outs]
-        for x in a_parts + b_parts + tuple(outs):
-            _sync(x)
-        _check(fn(m, n, k, *ptrs, *optr, *extra, 0))
-        return outs
-    a_parts = tuple(np.ascontiguousarray(x, dtype=np.float64) for x in a_parts)
-    b_parts = tuple(np.ascontiguousarray(x, dtype=np.float64) for x in b_parts)
-    if a_parts[0].ndim != 2 or b_parts[0].ndim != 2:
-        raise ValueError("A and B must be 2-D")
-    m, n, k = _shapes(a_parts, b_parts)
-    outs = list(out) if out is not None else [np.empty((m, n), dtype=np.float64) for _ in range(nout)]
-    for o in outs:
-        if not (isinstance(o, np.ndarray) and o.dtype == np.float64 and o.shape == (m, n) and o.flags.c_contiguous):
-            raise TypeError("out= must hold C-contiguous float64 arrays of the result's shape")
-    p = [x.ctypes.data for x in a_parts + b_parts + tuple(outs)]
-    _check(fn(m, n, k, *p, *extra, 1))
-    return outs
+def _call(entry, left, right, n_results, trailing, out):
+    """One product through `entry`: `left` and `right` are the parts of A and B (1 for FP64, 2 for double-double, ...)."""
+    left, right = list(left), list(right)
+    if len(left) != n_results or len(right) != n_results:
+        raise ValueError(f"this product takes {n_results} part(s) per operand, got {len(left)} and {len(right)}")
+    parts = left + right
+    on_device = [_DeviceSide.owns(x) for x in parts]
+    if any(on_device) and not all(on_device):
+        raise TypeError("operands must be all on the host or all on the device")
+    side = _DeviceSide if on_device[0] else _HostSide
+    if side is _HostSide:
+        parts = [np.ascontiguousarray(x, dtype=np.float64) for x in parts]
+    described = [side.describe(x, "an operand") for x in parts]
+    (rows, inner), (inner_b, cols) = described[0][0], described[len(left)][0]
+    if inner != inner_b:
+        raise ValueError(f"cannot multiply {rows} x {inner} by {inner_b} x {cols}")
+    for (shape, _), expected in zip(described, [(rows, inner)] * len(left) + [(inner, cols)] * len(right)):
+        if tuple(shape) != expected:
+            raise ValueError(f"every part of an operand needs the same shape: {tuple(shape)} against {expected}")
+    if out is None:
+        results = [side.result_like(parts[0], (rows, cols)) for _ in range(n_results)]
+    else:
+        results = list(out)
+        if len(results) != n_results or not all(side.owns(r) for r in results):
+            raise TypeError(f"out= needs {n_results} array(s) on the same side as the operands")
+        for r in results:
+            if side is _HostSide and not (isinstance(r, np.ndarray) and r.dtype == np.float64 and r.flags.c_contiguous):
+                raise TypeError("out= arrays must be C-contiguous float64 numpy arrays")
+            if tuple(side.describe(r, "out")[0]) != (rows, cols):
+                raise ValueError(f"out= arrays must have shape {(rows, cols)}")
+    for x in parts + results:
+        side.hand_over(x)
+    addresses = [p for _, p in described] + [side.describe(r, "out")[1] for r in results]
+    status = entry(rows, cols, inner, *addresses, *trailing, side.on_host_flag)
+    if status:
+        raise OzakiError(status)
+    return results
 
 
 def matmul(a, b, moduli=16, out=None):
-    """C = A B in FP64 from INT8 tensor cores; `moduli` in 8..16 (16: FP64 accuracy for exponent spreads up to 2^+-16)."""
-    return _run(_lib.ozb_dgemm, (a,), (b,), 1, (int(moduli),), None if out is None else (out,))[0]
+    """A @ B with FP64 accuracy. `moduli` (8..16) is the reference's accuracy/speed knob: 16 gives full FP64 accuracy for
+    entries spread over 2^+-16, fewer moduli are faster and coarser. `out`: an array to receive the result."""
+    return _call(_lib.ozb_dgemm, [a], [b], 1, [int(moduli)], None if out is None else [out])[0]
 
 
 def matmul_dd(a, b, out=None):
-    """(Ch, Cl) = (Ah + Al)(Bh + Bl) in double-double, 32 moduli. a and b are (hi, lo) pairs."""
-    return tuple(_run(_lib.ozb_ddgemm, tuple(a), tuple(b), 2, (), out))
+    """Double-double product: a = (hi, lo) and b = (hi, lo) pairs of float64 arrays; returns (Ch, Cl). 32 moduli."""
+    return tuple(_call(_lib.ozb_ddgemm, a, b, 2, [], out))
 
 
 def matmul_td(a, b, out=None):
-    """Triple-double product: exported for interface compatibility; this build raises OzakiError."""
-    return tuple(_run(_lib.ozb_tdgemm, tuple(a), tuple(b), 3, (), out))
+    """Triple-double product of (x0, x1, x2) triples. Kept for interface compatibility: this library does not build it
+    and the call raises OzakiError."""
+    return tuple(_call(_lib.ozb_tdgemm, a, b, 3, [], out))
 
 
 def device():
-    """Name, compute capability (e.g. 100), L2 size in KiB and SM count of the current CUDA device."""
-    name = ctypes.create_string_buffer(256)
-    sm, l2, sms = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
-    _check(_lib.ozb_device(name, 256, ctypes.byref(sm), ctypes.byref(l2), ctypes.byref(sms)))
-    return {"name": name.value.decode(), "sm": sm.value, "l2_kib": l2.value, "sms": sms.value}
+    """The current CUDA device as a dict: name, sm (10 * major + minor), l2_kib, sms."""
+    text = ctypes.create_string_buffer(256)
+    numbers = [ctypes.c_int() for _ in range(3)]
+    status = _lib.ozb_device(text, len(text), *[ctypes.byref(v) for v in numbers])
+    if status:
+        raise OzakiError(status)
+    return dict(zip(("name", "sm", "l2_kib", "sms"), [text.value.decode()] + [v.value for v in numbers]))
 
 
 def release():
-    """Free the device memory of the cached plans."""
+    """Give back the device memory held by the cached plans."""
     _lib.ozb_release()
 
 
+_BENCH_KINDS = {"fp64": 0, "dd": 1, "td": 2}
+
+
 def bench(n=4096, kind="fp64", reps=5):
-    """Median GPU time (ms) and FP64-equivalent TFLOPS of an n x n x n product on the device, transfers excluded."""
-    kinds = {"fp64": 0, "dd": 1, "td": 2}
-    ms = ctypes.c_double()
-    _check(_lib.ozb_bench(int(n), kinds[kind], int(reps), ctypes.byref(ms)))
-    return ms.value, 2.0 * n ** 3 / (ms.value * 1e-3) / 1e12
+    """The library's built-in timing of an n x n x n product with operands on the device: (median ms, FP64-equivalent
+    TFLOP/s). kind: "fp64", "dd" or "td"."""
+    if kind not in _BENCH_KINDS:
+        raise ValueError(f"kind must be one of {sorted(_BENCH_KINDS)}")
+    median = ctypes.c_double()
+    status = _lib.ozb_bench(int(n), _BENCH_KINDS[kind], int(reps), ctypes.byref(median))
+    if status:
+        raise OzakiError(status)
+    return median.value, 2.0 * float(n) ** 3 / (median.value * 1e-3) / 1e12
