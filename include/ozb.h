@@ -72,7 +72,8 @@ int ozb_modulus(int l);
 /* The reference's oz::Plan (src/ozaki2.cuh:116-132) as an opaque handle: workspaces for one (M, N, K, moduli) shape on
  * the device that is current at creation. */
 typedef struct ozb_plan ozb_plan;
-/* src/ozaki2.cuh:122-131 (oz::plan) */
+/* src/ozaki2.cuh:122-131 (oz::plan). The plan's workspaces live on the device that is current at this call; the
+ * computing ozb_plan_* calls return cudaErrorInvalidDevice (101) when made with another device current. */
 int ozb_plan_create(int M, int N, int K, int moduli, int maxbits, ozb_plan **out);
 /* src/ozaki2.cuh:132 (oz::release) */
 void ozb_plan_destroy(ozb_plan *p);

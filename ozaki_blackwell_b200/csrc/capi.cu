@@ -157,6 +157,12 @@ static cudaError_t gemm_chunks(ozb_plan *p, const int8_t *Br, int8_t *Cr, int n,
     return cudaSuccess;
 }
 
+// a plan's workspaces live on the device that was current when it was made: launching from another one would read them
+// through peer mappings at best
+static bool on_plan_device(const ozb_plan *p) {
+    int dev = -1;
+    return cudaGetDevice(&dev) == cudaSuccess && dev == p->dev;
+}
 static int plan_set_a(ozb_plan *p, const double *A, long long lda, cudaStream_t st) {
     p->last = st;
     return (int)scale_residues_rows(p->nm, A, p->M, p->K, lda, p->bits, p->sa, p->Ar, p->Kp, p->planeA, st);
@@ -576,39 +582,46 @@ OZB_API void ozb_plan_destroy(ozb_plan *p) {
 OZB_API int ozb_plan_dgemm(ozb_plan *p, const double *A, long long lda, const double *B, long long ldb, double *C, long long ldc,
                            void *stream) {
     if (!p || !A || !B || !C || lda < p->K || ldb < p->N || ldc < p->N) return OZB_EARG;
+    if (!on_plan_device(p)) return (int)cudaErrorInvalidDevice;
     std::lock_guard<std::mutex> g(mu);
     return plan_dgemm(p, A, lda, B, ldb, C, ldc, (cudaStream_t)stream);
 }
 OZB_API int ozb_plan_set_a(ozb_plan *p, const double *A, long long lda, void *stream) {
     if (!p || !A || lda < p->K) return OZB_EARG;
+    if (!on_plan_device(p)) return (int)cudaErrorInvalidDevice;
     std::lock_guard<std::mutex> g(mu);
     return plan_set_a(p, A, lda, (cudaStream_t)stream);
 }
 OZB_API int ozb_plan_panel(ozb_plan *p, const double *B, long long ldb, double *C, long long ldc, int j0, int ncols, void *stream) {
     if (!p || !B || !C || j0 < 0 || (j0 & 255) || ncols <= 0 || j0 + ncols > p->N || ldb < ncols || ldc < ncols) return OZB_EARG;
+    if (!on_plan_device(p)) return (int)cudaErrorInvalidDevice;
     std::lock_guard<std::mutex> g(mu);
     return plan_panel(p, B, ldb, C, ldc, j0, ncols, (cudaStream_t)stream, nullptr);
 }
 // B in chunks of rows (as it arrives from a broadcast or from the host), then the product with the prepared operands
 OZB_API int ozb_plan_b_begin(ozb_plan *p, void *stream) {
     if (!p) return OZB_EARG;
+    if (!on_plan_device(p)) return (int)cudaErrorInvalidDevice;
     std::lock_guard<std::mutex> g(mu);
     p->last = (cudaStream_t)stream;
     return (int)cudaMemsetAsync(p->colmax, 0, (size_t)p->N * 8, (cudaStream_t)stream);
 }
 OZB_API int ozb_plan_b_rows(ozb_plan *p, const double *Brows, long long ldb, int rows, void *stream) {
     if (!p || !Brows || rows <= 0 || rows > p->K || ldb < p->N) return OZB_EARG;
+    if (!on_plan_device(p)) return (int)cudaErrorInvalidDevice;
     std::lock_guard<std::mutex> g(mu);
     return (int)cols_absmax_accumulate(Brows, rows, p->N, ldb, p->colmax, (cudaStream_t)stream);
 }
 OZB_API int ozb_plan_b_finish(ozb_plan *p, const double *B, long long ldb, void *stream) {
     if (!p || !B || ldb < p->N) return OZB_EARG;
+    if (!on_plan_device(p)) return (int)cudaErrorInvalidDevice;
     std::lock_guard<std::mutex> g(mu);
     return (int)cols_residues_from_max(p->nm, B, p->K, p->N, ldb, p->bits, p->colmax, p->sb, p->Br, p->Kp, p->planeB, (cudaStream_t)stream);
 }
 // rows [k0, k0 + rows) of B with column maxima the caller holds (computed where the whole of B is, e.g. on another GPU)
 OZB_API int ozb_plan_b_rows_residues(ozb_plan *p, const double *Brows, long long ldb, int k0, int rows, const void *colmax, void *stream) {
     if (!p || !Brows || !colmax || rows <= 0 || k0 < 0 || (k0 & 127) || k0 + rows > p->K || ldb < p->N) return OZB_EARG;
+    if (!on_plan_device(p)) return (int)cudaErrorInvalidDevice;
     std::lock_guard<std::mutex> g(mu);
     p->last = (cudaStream_t)stream;
     return (int)cols_residues_from_max(p->nm, Brows, rows, p->N, ldb, p->bits, (const unsigned long long *)colmax, p->sb, p->Br + k0, p->Kp,
@@ -621,6 +634,7 @@ OZB_API int ozb_cols_absmax(const double *X, int rows, int cols, long long ldx, 
 }
 OZB_API int ozb_plan_multiply(ozb_plan *p, double *C, long long ldc, void *stream) {
     if (!p || !C || ldc < p->N) return OZB_EARG;
+    if (!on_plan_device(p)) return (int)cudaErrorInvalidDevice;
     std::lock_guard<std::mutex> g(mu);
     cudaStream_t st = (cudaStream_t)stream;
     p->last = st;

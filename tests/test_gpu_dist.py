@@ -66,5 +66,18 @@ def test_one_process_two_devices():
             torch.cuda.set_device(dev)
             got = g.gpu_dgemm(A, B, 16)
             assert g.same_bits(got, want), (dev, g.describe_mismatch(got, want))
+        # a plan belongs to the device it was made on: from another current device its calls are refused
+        import ctypes
+        from ozaki_blackwell_b200._lib import lib
+        torch.cuda.set_device(0)
+        plan = ctypes.c_void_p()
+        g.check(lib.ozb_plan_create(64, 64, 64, 16, 62, ctypes.byref(plan)))
+        a = torch.zeros((64, 64), dtype=torch.float64, device="cuda:0")
+        torch.cuda.set_device(1)
+        assert lib.ozb_plan_set_a(plan, g.ptr(a), 64, None) == 101      # cudaErrorInvalidDevice
+        torch.cuda.set_device(0)
+        g.check(lib.ozb_plan_set_a(plan, g.ptr(a), 64, None))
+        g.check(lib.ozb_plan_status(plan))
+        lib.ozb_plan_destroy(plan)
     finally:
         torch.cuda.set_device(0)
