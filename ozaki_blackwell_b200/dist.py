@@ -222,6 +222,8 @@ class RowShardedGemm:
         if self.world == 1:
             self.engine.full(a_local, b, c_local, self.compute)
             return c_local
+        if self.rank == self.src and b.stride(1) != 1:
+            b = b.contiguous()                      # the kernels take a row pitch, not a column stride
         if self.layout == "rows":
             return self._by_rows(a_local, b, c_local)
         # The source packs each panel (panel-major, contiguous) on a stream of its own, broadcasts it as soon as it is
