@@ -114,10 +114,18 @@ class CudaEngine:
         if code:
             raise RuntimeError(self._lib.ozb_error(code).decode())
 
+    @staticmethod
+    def _row_major(*tensors):
+        for t in tensors:
+            if t.dim() != 2 or t.stride(1) != 1 or t.dtype != torch.float64:
+                raise ValueError("operands must be two-dimensional float64 tensors with unit column stride")
+
     def set_a(self, a, stream):
+        self._row_major(a)
         self._check(self._lib.ozb_plan_set_a(self._plan, a.data_ptr(), a.stride(0), stream.cuda_stream))
 
     def panel(self, b_panel, c, j0, ncols, stream):
+        self._row_major(b_panel, c)
         c_ptr = c.data_ptr() + 8 * j0
         self._check(self._lib.ozb_plan_panel(self._plan, b_panel.data_ptr(), b_panel.stride(0), c_ptr, c.stride(0), j0, ncols,
                                              stream.cuda_stream))
@@ -139,9 +147,11 @@ class CudaEngine:
         self._check(self._lib.ozb_plan_b_finish(self._plan, b.data_ptr(), b.stride(0), stream.cuda_stream))
 
     def multiply(self, c, stream):
+        self._row_major(c)
         self._check(self._lib.ozb_plan_multiply(self._plan, c.data_ptr(), c.stride(0), stream.cuda_stream))
 
     def full(self, a, b, c, stream):
+        self._row_major(a, b, c)
         self._check(self._lib.ozb_plan_dgemm(self._plan, a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), c.data_ptr(),
                                              c.stride(0), stream.cuda_stream))
 
