@@ -113,15 +113,19 @@ int ozb_plan_status(ozb_plan *p);
  * created while the environment variable OZ_PROF is set starts with one slot and prints the reference's line on stderr
  * after every product (which synchronises). */
 int ozb_plan_profile(ozb_plan *p, int slots);
-/* Milliseconds of the product recorded in `slot`. A product is processed in column panels whose B-residue, GEMM and CRT
- * stages overlap on internal streams (environment variable OZ_PANELS = 1 keeps one panel and one stream), so the split
- * is: ms[0] start of the product to the start of the first GEMM (exposed scaling + residues), ms[1] sum of the GEMM
- * kernels' own durations, ms[2] end of the last GEMM to the end of the product (exposed CRT), ms[3] the whole product.
- * Waits for that product to finish. */
+/* Milliseconds of the product recorded in `slot`: ms[0] start of the product to the start of the first GEMM (exposed
+ * scaling + residues), ms[1] sum of the GEMM kernels' own durations, ms[2] end of the last GEMM to the end of the
+ * product (exposed CRT), ms[3] the whole product. By default a product is one column panel on the caller's stream and
+ * the three parts add up to ms[3]. A plan made while the environment variable OZ_PANELS is 2..8 cuts the columns into
+ * that many panels whose B-residue, GEMM and CRT stages overlap on internal streams (measured slower on B200, hence not
+ * the default); ms[1] is then the sum over the panels. Waits for that product to finish. */
 int ozb_plan_phase_ms(ozb_plan *p, int slot, float ms[4]);
 
 /* ozb_dgemm with leading dimensions, on device pointers, on a stream, without the final synchronisation. Uses the same
- * cached plan as ozb_dgemm. */
+ * cached plan as ozb_dgemm (one per precision, replaced when the shape changes). ozb_dgemm_ex, ozb_dgemm_norm and
+ * ozb_ddgemm_ex share that plan's workspaces: the library orders each such product after the previous one (an event
+ * per plan), so calls on different streams are safe but do not overlap; use ozb_plan_create for independent plans.
+ * A bounded wait that expired in one of these products is reported by ozb_status. */
 int ozb_dgemm_ex(int M, int N, int K, const double *A, long long lda, const double *B, long long ldb, double *C,
                  long long ldc, int moduli, void *stream);
 
@@ -190,8 +194,8 @@ int ozb_int8_peak(int iters, int pair, float *ms, double *tops);
  * waits, with a budget of budget_ms (1..2000), on a barrier that nothing completes. The expected return value is
  * OZB_ETIMEOUT: the wait gave up, raised the status word and the kernel returned normally; the context stays usable. */
 int ozb_selftest_wait_expiry(int budget_ms);
-/* Status of the stage calls above (they share one device status word per device): 0 or OZB_ETIMEOUT. Synchronises
- * the device. */
+/* Status of the stage calls above (they share one status word per device) and of the cached plans behind ozb_dgemm_ex,
+ * ozb_dgemm_norm and ozb_ddgemm_ex on the current device: 0 or OZB_ETIMEOUT. Synchronises the device. */
 int ozb_status(void);
 
 #ifdef __cplusplus

@@ -43,6 +43,8 @@ struct ozb_plan {
     // host operands (on_host = 1): device copies kept with the plan, three streams, one event pair per column panel
     double *hA, *hB, *hC;
     cudaStream_t sIn, sRun, sOut;
+    bool host_streams;               // sIn, sRun, sOut and their events are all there
+    cudaEvent_t evDone;              // end of the last asynchronous product queued on a cached plan (orders the next one after it)
     cudaEvent_t evIn[HOST_PANELS + 1], evRun[HOST_PANELS];
 };
 constexpr int MAXP = 8, EV_PER_SLOT = 2 + 2 * MAXP;   // start, end, and (start, end) of each panel's GEMM
@@ -73,6 +75,7 @@ static void plan_free(ozb_plan *p) {
     if (p->sOut) cudaStreamDestroy(p->sOut);
     for (auto &e : p->evIn) if (e) cudaEventDestroy(e);
     for (auto &e : p->evRun) if (e) cudaEventDestroy(e);
+    if (p->evDone) cudaEventDestroy(p->evDone);
     delete p;
 }
 
@@ -118,6 +121,7 @@ static int plan_make(int M, int N, int K, int nm, int maxbits, ozb_plan **out) {
     if (!e) e = cudaMalloc(&p->colmax, (size_t)N * 8);
     if (!e) e = cudaMalloc(&p->status, 256);
     if (!e) e = cudaMemset(p->status, 0, 256);
+    if (!e) e = cudaEventCreateWithFlags(&p->evDone, cudaEventDisableTiming);
     // panels: one by default; OZ_PANELS = 2..8 splits the columns and overlaps the stages of different panels
     p->panel_width = round_up(N, 256); p->panels = 1;
     {
@@ -236,6 +240,19 @@ static int plan_ddgemm(ozb_plan *p, const double *Ah, const double *Al, long lon
     return (int)e;
 }
 
+// device copies of host operands, kept with the plan: all three or none
+static cudaError_t host_buffers(ozb_plan *p) {
+    if (p->hA && p->hB && p->hC) return cudaSuccess;
+    const size_t M = p->M, N = p->N, K = p->K;
+    cudaFree(p->hA); cudaFree(p->hB); cudaFree(p->hC);
+    p->hA = p->hB = p->hC = nullptr;
+    cudaError_t e = cudaMalloc(&p->hA, M * K * 8);
+    if (!e) e = cudaMalloc(&p->hB, K * N * 8);
+    if (!e) e = cudaMalloc(&p->hC, M * N * 8);
+    if (e) { cudaFree(p->hA); cudaFree(p->hB); cudaFree(p->hC); p->hA = p->hB = p->hC = nullptr; cudaGetLastError(); }
+    return e;
+}
+
 // Host operands (python/capi.cu:37-48,82-88 stage everything, compute, copy back). Here the three phases overlap and every
 // copy is contiguous: B goes first, in chunks of rows whose column maxima are taken as they land; once B is complete its
 // residues are formed, and A follows in blocks of rows. A block of rows of C needs only its rows of A (row scales are
@@ -246,19 +263,24 @@ static int plan_ddgemm(ozb_plan *p, const double *Ah, const double *Al, long lon
 static int plan_dgemm_host(ozb_plan *p, const double *A, const double *B, double *C) {
     const size_t M = p->M, N = p->N, K = p->K;
     cudaError_t e = cudaSuccess;
-    if (!p->hA) {
-        e = cudaMalloc(&p->hA, M * K * 8);
-        if (!e) e = cudaMalloc(&p->hB, K * N * 8);
-        if (!e) e = cudaMalloc(&p->hC, M * N * 8);
-        if (e) return (int)e;
-    }
-    if (!p->sIn) {
+    if ((e = host_buffers(p))) return (int)e;
+    if (!p->host_streams) {   // all or nothing: a partial set-up is torn down, so the next call starts from scratch
         e = cudaStreamCreateWithFlags(&p->sIn, cudaStreamNonBlocking);
         if (!e) e = cudaStreamCreateWithFlags(&p->sRun, cudaStreamNonBlocking);
         if (!e) e = cudaStreamCreateWithFlags(&p->sOut, cudaStreamNonBlocking);
         for (auto &ev : p->evIn) if (!e) e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
         for (auto &ev : p->evRun) if (!e) e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
-        if (e) return (int)e;
+        if (e) {
+            if (p->sIn) cudaStreamDestroy(p->sIn);
+            if (p->sRun) cudaStreamDestroy(p->sRun);
+            if (p->sOut) cudaStreamDestroy(p->sOut);
+            p->sIn = p->sRun = p->sOut = nullptr;
+            for (auto &ev : p->evIn) if (ev) { cudaEventDestroy(ev); ev = nullptr; }
+            for (auto &ev : p->evRun) if (ev) { cudaEventDestroy(ev); ev = nullptr; }
+            cudaGetLastError();
+            return (int)e;
+        }
+        p->host_streams = true;
     }
     static const int want = [] { const char *env = getenv("OZ_HOST_PANELS"); return env && *env ? atoi(env) : 0; }();
     auto pieces = [&](size_t extent) {   // about 512 rows per piece, at most 16 (measured on B200: 16 beats 8 and 4 at n = 8192)
@@ -355,6 +377,13 @@ int plan_for(int which, int M, int N, int K, int nm, int maxbits, ozb_plan **out
     *out = c.p;
     return 0;
 }
+// The asynchronous entry points that use a cached plan share its workspaces: a product queued on one stream must not
+// start before the previous one, possibly queued on another stream, has finished with them.
+template <class F> int ordered_on_cached_plan(ozb_plan *p, cudaStream_t st, F &&enqueue) {
+    if (cudaError_t e = cudaStreamWaitEvent(st, p->evDone, 0)) return (int)e;
+    if (int e = enqueue()) return e;
+    return (int)cudaEventRecord(p->evDone, st);
+}
 int finish() { const int e = (int)cudaDeviceSynchronize(); return e ? e : (int)cudaGetLastError(); }   // python/capi.cu:49
 int *status_word() {
     int dev = 0;
@@ -420,13 +449,8 @@ OZB_API int ozb_dgemm(int M, int N, int K, const double *A, const double *B, dou
         return plan_status(p);
     }
     const size_t la = (size_t)M * K * 8, lb = (size_t)K * N * 8, lc = (size_t)M * N * 8;
-    int e = 0;
-    if (!p->hA) {
-        e = (int)cudaMalloc(&p->hA, la);
-        if (!e) e = (int)cudaMalloc(&p->hB, lb);
-        if (!e) e = (int)cudaMalloc(&p->hC, lc);
-        if (e) { cudaFree(p->hA); cudaFree(p->hB); cudaFree(p->hC); p->hA = p->hB = p->hC = nullptr; return e; }
-    }
+    int e = (int)host_buffers(p);
+    if (e) return e;
     e = (int)cudaMemcpy(p->hA, A, la, cudaMemcpyHostToDevice);
     if (!e) e = (int)cudaMemcpy(p->hB, B, lb, cudaMemcpyHostToDevice);
     if (!e) e = plan_dgemm(p, p->hA, K, p->hB, N, p->hC, N, 0);
@@ -474,7 +498,7 @@ OZB_API int ozb_ddgemm_ex(int M, int N, int K, const double *Ah, const double *A
     std::lock_guard<std::mutex> g(mu);
     ozb_plan *p;
     if (int e = plan_for(1, M, N, K, moduli, 106, &p)) return e;
-    return plan_ddgemm(p, Ah, Al, lda, Bh, Bl, ldb, Ch, Cl, ldo, mode, (cudaStream_t)stream);
+    return ordered_on_cached_plan(p, (cudaStream_t)stream, [&] { return plan_ddgemm(p, Ah, Al, lda, Bh, Bl, ldb, Ch, Cl, ldo, mode, (cudaStream_t)stream); });
 }
 
 OZB_API int ozb_tdgemm(int M, int N, int K, const double *, const double *, const double *, const double *, const double *,
@@ -677,7 +701,7 @@ OZB_API int ozb_dgemm_ex(int M, int N, int K, const double *A, long long lda, co
     std::lock_guard<std::mutex> g(mu);
     ozb_plan *p;
     if (int e = plan_for(0, M, N, K, moduli, 62, &p)) return e;
-    return plan_dgemm(p, A, lda, B, ldb, C, ldc, (cudaStream_t)stream);
+    return ordered_on_cached_plan(p, (cudaStream_t)stream, [&] { return plan_dgemm(p, A, lda, B, ldb, C, ldc, (cudaStream_t)stream); });
 }
 
 // bench/oz_strassen.cu:74-97,247 -- the product with the reference's optional 2-norm scales: beta = floor((log2 P - 1.001) / 2)
@@ -694,11 +718,13 @@ OZB_API int ozb_dgemm_norm(int M, int N, int K, const double *A, long long lda, 
     if (beta > 62) beta = 62;
     cudaStream_t st = (cudaStream_t)stream;
     p->last = st;
-    cudaError_t e = norm_scale_residues_rows(p->nm, A, M, K, lda, beta, p->sa, p->Ar, p->Kp, p->planeA, st);
-    if (!e) e = norm_scale_residues_cols(p->nm, B, K, N, ldb, beta, p->sb, p->Br, p->Kp, p->planeB, st);
-    if (!e) e = gemm_chunks(p, p->Br, p->Cr, N, st);
-    if (!e) e = crt_from_i8(p->nm, p->Cr, p->planeC, M, N, p->Np, p->sa, p->sb, C, ldc, st);
-    return (int)e;
+    return ordered_on_cached_plan(p, st, [&] {
+        cudaError_t e = norm_scale_residues_rows(p->nm, A, M, K, lda, beta, p->sa, p->Ar, p->Kp, p->planeA, st);
+        if (!e) e = norm_scale_residues_cols(p->nm, B, K, N, ldb, beta, p->sb, p->Br, p->Kp, p->planeB, st);
+        if (!e) e = gemm_chunks(p, p->Br, p->Cr, N, st);
+        if (!e) e = crt_from_i8(p->nm, p->Cr, p->planeC, M, N, p->Np, p->sa, p->sb, C, ldc, st);
+        return (int)e;
+    });
 }
 OZB_API int ozb_scale_residues_rows(int moduli, const double *X, int rows, int len, long long ldx, int bits, int *s, int8_t *R,
                                     int ld, size_t plane, void *stream) {
@@ -770,7 +796,13 @@ OZB_API int ozb_selftest_wait_expiry(int budget_ms) {
 }
 OZB_API int ozb_status(void) {
     if (int e = (int)cudaDeviceSynchronize()) return e;
+    std::lock_guard<std::mutex> g(mu);
     int *st = status_word();
     if (!st) return (int)cudaErrorMemoryAllocation;
-    return read_status(st);
+    int r = read_status(st);
+    int dev = -1;
+    cudaGetDevice(&dev);
+    for (Cache &c : cache)   // the cached plans of ozb_dgemm_ex / ozb_dgemm_norm / ozb_ddgemm_ex have status words of their own
+        if (c.p && c.p->dev == dev) { const int q = read_status(c.p->status); if (!r) r = q; }
+    return r;
 }

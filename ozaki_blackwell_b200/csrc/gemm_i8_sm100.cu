@@ -118,6 +118,7 @@ struct Params {
     int accumulate;               // fused mode: add the residues already stored in C (a previous K chunk) before reducing
     void *C;                      // int32 [Z][M][ldc] or int8 [Z][M][ldc]
     long long ldc;                // row pitch of C in elements
+    int wcols;                    // fused mode: columns of this launch's C that may be written, N rounded up to 16 (whole 16-byte pieces)
     size_t plane_c;               // plane pitch of C in elements
     int *status;                  // device word: set to 1 when a wait timed out
     int *counter;                 // two-CTA kernel: next work item, zeroed before the launch
@@ -155,8 +156,8 @@ __device__ __forceinline__ void store_piece(const Params &p, const ModConsts &mc
         int8_t *dst = reinterpret_cast<int8_t *>(p.C) + (size_t)z * p.plane_c + (size_t)row * p.ldc + col;
         uint32_t prev[8] = {};
         if (p.accumulate) {   // residues of the K chunks before this one: residues add, |sum| stays far below 2^31
-            if (col + 16 <= p.ldc) { const uint4 q = *reinterpret_cast<const uint4 *>(dst); prev[0] = q.x; prev[1] = q.y; prev[2] = q.z; prev[3] = q.w; }
-            if (col + 32 <= p.ldc) { const uint4 q = *reinterpret_cast<const uint4 *>(dst + 16); prev[4] = q.x; prev[5] = q.y; prev[6] = q.z; prev[7] = q.w; }
+            if (col + 16 <= p.wcols) { const uint4 q = *reinterpret_cast<const uint4 *>(dst); prev[0] = q.x; prev[1] = q.y; prev[2] = q.z; prev[3] = q.w; }
+            if (col + 32 <= p.wcols) { const uint4 q = *reinterpret_cast<const uint4 *>(dst + 16); prev[4] = q.x; prev[5] = q.y; prev[6] = q.z; prev[7] = q.w; }
         }
         uint32_t o[8];
 #pragma unroll
@@ -171,8 +172,8 @@ __device__ __forceinline__ void store_piece(const Params &p, const ModConsts &mc
             }
             o[g] = pack_low_bytes(x[0], x[1], x[2], x[3]);
         }
-        if (col + 16 <= p.ldc) *reinterpret_cast<uint4 *>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
-        if (col + 32 <= p.ldc) *reinterpret_cast<uint4 *>(dst + 16) = make_uint4(o[4], o[5], o[6], o[7]);
+        if (col + 16 <= p.wcols) *reinterpret_cast<uint4 *>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
+        if (col + 32 <= p.wcols) *reinterpret_cast<uint4 *>(dst + 16) = make_uint4(o[4], o[5], o[6], o[7]);
     } else {
         int32_t *dst = reinterpret_cast<int32_t *>(p.C) + (size_t)z * p.plane_c + (size_t)row * p.ldc + col;
         if (col + 32 <= p.N && ((p.ldc | p.plane_c) & 3) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0) {
@@ -762,6 +763,7 @@ cudaError_t gemm_i8_planes(const int8_t *A, const int8_t *Bt, void *C, int M, in
     p.first_modulus = first_modulus;
     p.accumulate = accumulate;
     p.C = C; p.ldc = ldc; p.plane_c = pc; p.status = status;
+    p.wcols = (N + 15) / 16 * 16;   // C may be a column window of wider planes: nothing beyond this launch's own pieces is touched
     if (sms <= 0) {
         int dev;
         if ((e = cudaGetDevice(&dev))) return e;
