@@ -26,7 +26,9 @@ enum {
     OZB_EARCH = 10003,    /* python/capi.cu:17 -- unsupported GPU; here: anything that is not compute capability 10.x */
     OZB_ETIMEOUT = 10004, /* addition: a bounded wait inside the GEMM kernel expired; the result is not valid */
     OZB_ENOTBUILT = 10005,/* addition: the entry point exists for ABI compatibility but this build has no kernel for it */
-    OZB_ESIZE = 10006     /* addition: a size exceeds a stated fixed limit of the entry point */
+    OZB_ESIZE = 10006,    /* addition: a size exceeds a stated fixed limit of the entry point */
+    OZB_ECOMM = 10007,    /* addition: the exchange between GPUs failed or did not finish in time; the communicator was aborted */
+    OZB_ENCCL = 10008     /* addition: the NCCL library (libnccl.so.2) could not be loaded */
 };
 
 /* ---- the reference's ABI ------------------------------------------------------------------------------------- */
@@ -120,6 +122,10 @@ int ozb_plan_profile(ozb_plan *p, int slots);
  * that many panels whose B-residue, GEMM and CRT stages overlap on internal streams (measured slower on B200, hence not
  * the default); ms[1] is then the sum over the panels. Waits for that product to finish. */
 int ozb_plan_phase_ms(ozb_plan *p, int slot, float ms[4]);
+/* The same product kernel by kernel (one-panel plans only, OZB_EARG otherwise) -- what the reference's OZ_PROF line and its
+ * phase benchmark report (src/ozaki2.cuh:147-152, bench/phases.cu:21-30): ms[0] scales + residues of A, ms[1] column maxima
+ * of B, ms[2] residues of B, ms[3] the INT8 GEMM launches, ms[4] the reconstruction. */
+int ozb_plan_kernel_ms(ozb_plan *p, int slot, float ms[5]);
 
 /* ozb_dgemm with leading dimensions, on device pointers, on a stream, without the final synchronisation. Uses the same
  * cached plan as ozb_dgemm (one per precision, replaced when the shape changes). ozb_dgemm_ex, ozb_dgemm_norm and
@@ -128,6 +134,43 @@ int ozb_plan_phase_ms(ozb_plan *p, int slot, float ms[4]);
  * A bounded wait that expired in one of these products is reported by ozb_status. */
 int ozb_dgemm_ex(int M, int N, int K, const double *A, long long lda, const double *B, long long ldb, double *C,
                  long long ldc, int moduli, void *stream);
+
+/* ---- several GPUs of one machine --------------------------------------------------------------------------------
+ * No counterpart in the reference, which is single-GPU; the entry shape extended is ozb_dgemm (python/capi.cu:77-89).
+ * The product is partitioned by output row blocks: every rank (one per GPU) owns a block of rows of A and produces the
+ * same rows of C; B is held by one rank and broadcast once per product over NVLink by NCCL (loaded at run time), nothing
+ * else is exchanged, and the rows every rank returns are bit-identical to the same rows of the single-GPU product. */
+
+/* One process, `ndev` GPUs (devices 0 .. ndev-1): C = A B as ozb_dgemm computes it. on_host = 1: A, B, C are host
+ * pointers (pinned memory lets every GPU stream its rows while it computes). on_host = 0: device pointers on the calling
+ * thread's current device, which must be one of the ndev; the other GPUs get their rows by peer copies. Synchronous.
+ * The communicators and workspaces are cached until ozb_mg_release or a call with another ndev. */
+int ozb_dgemm_mg(int M, int N, int K, const double *A, const double *B, double *C, int moduli, int on_host, int ndev);
+void ozb_mg_release(void);
+
+/* One rank per process (or thread). Rendezvous: one rank fills a 128-byte id with ozb_mg_unique_id and hands it to the
+ * others by any means; every rank then calls ozb_mg_create with its device current. timeout_ms (0: 30 s) bounds every
+ * host-side wait of the handle: setting up, queueing a transfer, waiting for a product. When it runs out -- a peer never
+ * joined or is gone -- the communicator is aborted and the call returns OZB_ECOMM, as does every later call on the
+ * handle; the CUDA context stays usable. */
+#define OZB_MG_ID_BYTES 128
+typedef struct ozb_mg ozb_mg;
+int ozb_mg_unique_id(void *id);
+int ozb_mg_create(int world, int rank, const void *id, int timeout_ms, ozb_mg **out);
+void ozb_mg_destroy(ozb_mg *g);
+/* This rank's rows: C_local (m_local x N) = A_local (m_local x K) B (K x N). B is read on rank `root` only (others may
+ * pass NULL). on_host = 0: device pointers with leading dimensions, asynchronous on `stream` and on a communication
+ * stream of the handle; ozb_mg_wait tells how the product ended. on_host = 1: dense host pointers (lda = K, ldb = N,
+ * ldc = N), copies pipelined with the broadcast and the computation, synchronous. Every rank must make the same
+ * sequence of calls with the same N, K, moduli and root. */
+int ozb_mg_dgemm(ozb_mg *g, int m_local, int N, int K, const double *A, long long lda, const double *B, long long ldb, double *C,
+                 long long ldc, int moduli, int root, int on_host, void *stream);
+/* Waits (within the handle's budget) for the last product queued on the handle: 0, OZB_ETIMEOUT (a bounded wait inside a
+ * GEMM kernel expired) or OZB_ECOMM. */
+int ozb_mg_wait(ozb_mg *g);
+/* How the last product moved B: *layout 0 = in one transfer, 1 = column maxima first, then pieces of rows consumed as
+ * they land; *pieces = number of transfers of B. */
+int ozb_mg_info(ozb_mg *g, int *layout, int *pieces);
 
 /* bench/oz_strassen.cu:74-97,247 (scales_norm) -- C = A B with the reference's optional scaling from the 2-norm of each row
  * of A and column of B instead of its largest entry (Cauchy-Schwarz bounds the integer products without K, so more bits

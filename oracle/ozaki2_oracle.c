@@ -24,6 +24,9 @@
  * seeds) and requires the published error table; on a GPU machine tests/test_reference_parity.py compares it bit for bit
  * with the reference's own kernels built from the reference sources.
  */
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 #include <math.h>
 #include <stdint.h>
 #include <stdlib.h>
@@ -35,6 +38,18 @@
 static const int MODULI[OZ_MAXM] = {256, 255, 253, 251, 247, 241, 239, 233, 229, 227, 223, 217, 211, 199, 197, 193,
                                     191, 181, 179, 173, 167, 163, 157, 151, 149, 139, 137, 131, 127, 113, 109, 107,
                                     103, 101, 97,  89,  83,  79,  73,  71,  67,  61,  59,  53,  47,  43,  41,  37,  29};
+
+/* Number of OpenMP threads of the checker's loops (0: leave as is). Launchers such as torch.distributed.run export
+ * OMP_NUM_THREADS=1 to their children; a caller that wants every host core back says so here. Returns the count in use. */
+int oz_oracle_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
+#else
+    (void)n;
+    return 1;
+#endif
+}
 
 int oz_oracle_modulus(int l) { return (l >= 0 && l < OZ_MAXM) ? MODULI[l] : 0; }
 

@@ -12,6 +12,7 @@
 #include "../../include/ozb.h"
 #include "oz_common.cuh"
 #include "oz_kernels.h"
+#include "oz_plan.h"
 
 #define OZB_API extern "C" __attribute__((visibility("default")))
 #ifndef OZB_VERSION
@@ -23,33 +24,13 @@ using namespace ozk;
 // ---------------------------------------------------------------------------------------------------------------
 // plan
 // ---------------------------------------------------------------------------------------------------------------
-constexpr int HOST_PANELS = 32;
-struct ozb_plan {
-    int M, N, K, nm, bits, maxbits, dev;   // dev: the device the workspaces live on
-    int Kp, Np;                      // pitch of the residue planes of A and B (bytes); pitch of the product planes (bytes)
-    size_t planeA, planeB, planeC;   // plane pitches in bytes
-    int8_t *Ar, *Br, *Cr;
-    int *sa, *sb, *status;
-    unsigned long long *colmax;
-    cudaStream_t last;
-    bool env_prof;                   // OZ_PROF set: one line per product on stderr, as the reference does
-    int slots, calls;                // event ring: EV_PER_SLOT events per slot, slot = call number mod slots
-    cudaEvent_t *ev;
-    // column panels of one product: B's residues (stream s1), the GEMMs (caller's stream) and the CRT (stream s2) of
-    // different panels run side by side; panels = 1 keeps everything on the caller's stream
-    int panels, panel_width;
-    cudaStream_t s1, s2;
-    cudaEvent_t evFork, evJoin, evB[8], evG[8];
-    // host operands (on_host = 1): device copies kept with the plan, three streams, one event pair per column panel
-    double *hA, *hB, *hC;
-    cudaStream_t sIn, sRun, sOut;
-    bool host_streams;               // sIn, sRun, sOut and their events are all there
-    cudaEvent_t evDone;              // end of the last asynchronous product queued on a cached plan (orders the next one after it)
-    cudaEvent_t evIn[HOST_PANELS + 1], evRun[HOST_PANELS];
-};
-constexpr int MAXP = 8, EV_PER_SLOT = 2 + 2 * MAXP;   // start, end, and (start, end) of each panel's GEMM
-
 static int round_up(int x, int to) { return (x + to - 1) / to * to; }
+static int plan_make(int M, int N, int K, int nm, int maxbits, ozb_plan **out);
+static void plan_free(ozb_plan *p);
+static int read_status(int *dev_words);
+int ozb_plan_make_internal(int M, int N, int K, int nm, int maxbits, ozb_plan **out) { return plan_make(M, N, K, nm, maxbits, out); }
+void ozb_plan_free_internal(ozb_plan *p) { plan_free(p); }
+int ozb_read_status_words(int *dev_words) { return read_status(dev_words); }
 
 static int bits_for_impl(int nm, int K, int maxbits) {   // src/ozaki2.cuh:101-108, with the abort turned into -1
     double log2P = 0;
@@ -104,6 +85,20 @@ static int plan_phase_ms(ozb_plan *p, int slot, float ms[4]) {
     return (int)e;
 }
 
+// the kernels of a one-panel product, one by one: ms[0] residues of A (row_scale_residues), ms[1] column maxima of B
+// (memset + col_absmax), ms[2] residues of B (col_residues_t), ms[3] the GEMM launches, ms[4] the reconstruction (crt_kernel)
+static int plan_kernel_ms(ozb_plan *p, int slot, float ms[5]) {
+    if (slot < 0 || slot >= p->slots || slot >= p->calls || p->panels != 1) return OZB_EARG;
+    cudaEvent_t *ev = p->ev + EV_PER_SLOT * slot;
+    if (cudaError_t e = cudaEventSynchronize(ev[1])) return (int)e;
+    cudaError_t e = cudaEventElapsedTime(&ms[0], ev[0], ev[EV_ROWS]);
+    if (!e) e = cudaEventElapsedTime(&ms[1], ev[EV_ROWS], ev[EV_ABSMAX]);
+    if (!e) e = cudaEventElapsedTime(&ms[2], ev[EV_ABSMAX], ev[2]);
+    if (!e) e = cudaEventElapsedTime(&ms[3], ev[2], ev[3]);
+    if (!e) e = cudaEventElapsedTime(&ms[4], ev[3], ev[1]);
+    return (int)e;
+}
+
 static int plan_make(int M, int N, int K, int nm, int maxbits, ozb_plan **out) {
     ozb_plan *p = new ozb_plan();
     memset(p, 0, sizeof *p);
@@ -144,21 +139,29 @@ static int plan_make(int M, int N, int K, int nm, int maxbits, ozb_plan **out) {
     return 0;
 }
 
-// The fused GEMMs of one column panel. A long K is cut into chunks of about 8192: within one chunk the A band and the B
-// panels that the resident CTAs share fit the L2 cache, whereas at K = 32768 they do not (measured: 1.8 instead of 3.2
-// POP/s, the kernel turns HBM-bound); later chunks add to the residues the earlier ones stored.
-static cudaError_t gemm_chunks(ozb_plan *p, const int8_t *Br, int8_t *Cr, int n, cudaStream_t st, int i0 = 0, int m = -1) {
+// The fused GEMMs of one column panel over the inner range [k0, k0 + klen). A long range is cut into chunks of about 8192:
+// within one chunk the A band and the B panels that the resident CTAs share fit the L2 cache, whereas at K = 32768 they do
+// not (measured: 1.8 instead of 3.2 POP/s, the kernel turns HBM-bound); later chunks add to the residues the earlier ones
+// stored. `accumulate` says whether the first chunk already finds residues of an earlier part of K in Cr.
+static cudaError_t gemm_range(ozb_plan *p, const int8_t *Br, int8_t *Cr, int n, cudaStream_t st, int i0, int m, int k0, int klen,
+                              int accumulate) {
     if (m < 0) m = p->M;   // rows [i0, i0 + m) of A and C
     static const int target = [] { const char *env = getenv("OZ_KCHUNK"); const int v = env && *env ? atoi(env) : 0; return v >= 1024 ? v : 8192; }();
-    const int chunks = p->K > target + target / 2 ? (p->K + target - 1) / target : 1;
-    const int kc = round_up((p->K + chunks - 1) / chunks, 128);
-    for (int k0 = 0, i = 0; k0 < p->K; k0 += kc, i++) {
-        const int klen = p->K - k0 < kc ? p->K - k0 : kc;
-        cudaError_t e = gemm_i8_planes(p->Ar + (size_t)i0 * p->Kp + k0, Br + k0, Cr + (size_t)i0 * p->Np, m, n, klen, p->nm, p->Kp, p->Kp,
-                                       p->Np, p->planeA, p->planeB, p->planeC, 1, 0, p->status, 0, st, i > 0);
+    const int chunks = klen > target + target / 2 ? (klen + target - 1) / target : 1;
+    const int kc = round_up((klen + chunks - 1) / chunks, 128);
+    for (int k = k0, i = 0; k < k0 + klen; k += kc, i++) {
+        const int len = k0 + klen - k < kc ? k0 + klen - k : kc;
+        cudaError_t e = gemm_i8_planes(p->Ar + (size_t)i0 * p->Kp + k, Br + k, Cr + (size_t)i0 * p->Np, m, n, len, p->nm, p->Kp, p->Kp,
+                                       p->Np, p->planeA, p->planeB, p->planeC, 1, 0, p->status, 0, st, accumulate || i > 0);
         if (e) return e;
     }
     return cudaSuccess;
+}
+static cudaError_t gemm_chunks(ozb_plan *p, const int8_t *Br, int8_t *Cr, int n, cudaStream_t st, int i0 = 0, int m = -1) {
+    return gemm_range(p, Br, Cr, n, st, i0, m, 0, p->K, 0);
+}
+cudaError_t ozb_plan_gemm_range(ozb_plan *p, int n, int k0, int klen, int accumulate, cudaStream_t st, int i0, int m) {
+    return gemm_range(p, p->Br, p->Cr, n, st, i0, m, k0, klen, accumulate);
 }
 
 // a plan's workspaces live on the device that was current when it was made: launching from another one would read them
@@ -195,11 +198,18 @@ static int plan_dgemm(ozb_plan *p, const double *A, long long lda, const double 
     if (ev) cudaEventRecord(ev[0], st);
     if (multi) { cudaEventRecord(p->evFork, st); cudaStreamWaitEvent(s1, p->evFork, 0); }
     cudaError_t e = scale_residues_rows(p->nm, A, p->M, p->K, lda, p->bits, p->sa, p->Ar, p->Kp, p->planeA, st);
-    for (int q = 0; q < p->panels && !e; q++) {   // B: maxima + residues of every panel, queued on s1 ahead of the GEMMs
+    if (ev && !multi) cudaEventRecord(ev[EV_ROWS], st);
+    if (!multi && !e) {   // one panel: the two passes over B as separate calls, with a timing mark between them
+        e = cudaMemsetAsync(p->colmax, 0, (size_t)p->N * 8, st);
+        if (!e) e = cols_absmax_accumulate(B, p->K, p->N, ldb, p->colmax, st);
+        if (ev) cudaEventRecord(ev[EV_ABSMAX], st);
+        if (!e) e = cols_residues_from_max(p->nm, B, p->K, p->N, ldb, p->bits, p->colmax, p->sb, p->Br, p->Kp, p->planeB, st);
+    }
+    for (int q = 0; multi && q < p->panels && !e; q++) {   // B: maxima + residues of every panel, queued on s1 ahead of the GEMMs
         const int j0 = q * p->panel_width, n = (p->N - j0 < p->panel_width) ? p->N - j0 : p->panel_width;
         e = scale_residues_cols(p->nm, B + j0, p->K, n, ldb, p->bits, p->colmax + j0, p->sb + j0, p->Br + (size_t)j0 * p->Kp, p->Kp,
                                 p->planeB, s1);
-        if (multi && !e) e = cudaEventRecord(p->evB[q], s1);
+        if (!e) e = cudaEventRecord(p->evB[q], s1);
     }
     for (int q = 0; q < p->panels && !e; q++) {
         const int j0 = q * p->panel_width, n = (p->N - j0 < p->panel_width) ? p->N - j0 : p->panel_width;
@@ -406,6 +416,8 @@ OZB_API const char *ozb_error(int e) {
     case OZB_ETIMEOUT: return "a bounded wait inside the INT8 GEMM kernel expired; the result is not valid";
     case OZB_ENOTBUILT: return "this entry point is exported for ABI compatibility but not built in this library";
     case OZB_ESIZE: return "a size exceeds the fixed limit of this entry point";
+    case OZB_ECOMM: return "the exchange between GPUs failed or did not finish in time; the communicator was aborted";
+    case OZB_ENCCL: return "the NCCL library (libnccl.so.2) could not be loaded";
     default: return cudaGetErrorString((cudaError_t)e);
     }
 }
@@ -692,6 +704,11 @@ OZB_API int ozb_plan_phase_ms(ozb_plan *p, int slot, float ms[4]) {
     if (!p || !ms) return OZB_EARG;
     std::lock_guard<std::mutex> g(mu);
     return plan_phase_ms(p, slot, ms);
+}
+OZB_API int ozb_plan_kernel_ms(ozb_plan *p, int slot, float ms[5]) {
+    if (!p || !ms) return OZB_EARG;
+    std::lock_guard<std::mutex> g(mu);
+    return plan_kernel_ms(p, slot, ms);
 }
 
 OZB_API int ozb_dgemm_ex(int M, int N, int K, const double *A, long long lda, const double *B, long long ldb, double *C,

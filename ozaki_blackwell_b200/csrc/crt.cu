@@ -33,8 +33,8 @@ template <int NM, int E>
 __device__ __forceinline__ void garner_digits(uint32_t (&X)[E][(NM + 3) / 4]) {
     static_for<1, NM>([&](auto L) {   // digit 0 is the residue mod 256 itself
         constexpr int l = decltype(L)::value;
-        constexpr int lift = lift_of(l, GARNER_BOUND);
-        static_assert(magic_ok(l, (uint64_t)lift + GARNER_BOUND), "multiply-high reduction out of range");
+        constexpr int lift = lift_of(l, GARNER_BOUND) - half_of(l);   // a multiple of m_l; the balancing shift is folded into balanced_magic
+        static_assert(lift > GARNER_BOUND && magic_ok(l, (uint64_t)lift + half_of(l) + GARNER_BOUND), "multiply-high reduction out of range");
         int acc[E];
 #pragma unroll
         for (int e = 0; e < E; e++) acc[e] = lift;
@@ -49,29 +49,29 @@ __device__ __forceinline__ void garner_digits(uint32_t (&X)[E][(NM + 3) / 4]) {
         constexpr uint32_t sel = l % 4 == 0 ? 0x3214u : l % 4 == 1 ? 0x3240u : l % 4 == 2 ? 0x3410u : 0x4210u;
 #pragma unroll
         for (int e = 0; e < E; e++) {
-            const uint32_t xl = mod_magic<l>((uint32_t)acc[e]) - (uint32_t)half_of(l);   // balanced digit, low byte
+            const uint32_t xl = balanced_magic<l>((uint32_t)acc[e]);                     // balanced digit, low byte
             X[e][l / 4] = __byte_perm(X[e][l / 4], xl, sel);                             // byte l%4 <- xl
         }
     });
 }
 
-// digit l of a packed word as a double: sign-extend the byte (one permute), then the 2^52 + 2^31 trick (one xor, one add)
+// digit l of a packed word of BIASED digits (x + 128, an unsigned byte) as a double: the byte moved into the low word of
+// 2^52 (one permute), minus 2^52 + 128 (one add)
 template <int B>
-__device__ __forceinline__ double digit_to_double(uint32_t word) {
-    constexpr uint32_t sel = B == 0 ? 0x8880u : B == 1 ? 0x9991u : B == 2 ? 0xAAA2u : 0xBBB3u;   // byte B, sign-replicated above it
-    uint32_t v;   // prmt: bit 3 of a selector nibble replicates the sign bit of the selected byte over the whole result byte
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(v) : "r"(word), "r"(0u), "r"(sel));
-    v ^= 0x80000000u;
-    return __hiloint2double(0x43300000, (int)v) - 4503601774854144.0;                            // 2^52 + 2^31
+__device__ __forceinline__ double digit_to_double(uint32_t biased) {
+    return __hiloint2double(0x43300000, (int)__byte_perm(biased, 0u, 0x4440u + B)) - 4503599627370624.0;   // 2^52 + 128
 }
 
 // the reference's Horner loop (src/ozaki2.cuh:93-95) on the packed digits of one element
 template <int NM>
 __device__ __forceinline__ double horner(const uint32_t (&X)[(NM + 3) / 4]) {
-    double y = digit_to_double<(NM - 1) % 4>(X[(NM - 1) / 4]);
+    uint32_t Bx[(NM + 3) / 4];
+#pragma unroll
+    for (int g = 0; g < (NM + 3) / 4; g++) Bx[g] = X[g] ^ 0x80808080u;   // int8 digits -> biased bytes, four at a time
+    double y = digit_to_double<(NM - 1) % 4>(Bx[(NM - 1) / 4]);
     static_for<1, NM>([&](auto I) {
         constexpr int l = NM - 1 - decltype(I)::value;
-        y = fma(y, (double)modulus(l), digit_to_double<l % 4>(X[l / 4]));
+        y = fma(y, (double)modulus(l), digit_to_double<l % 4>(Bx[l / 4]));
     });
     return y;
 }

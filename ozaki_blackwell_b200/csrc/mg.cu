@@ -1,0 +1,520 @@
+// mg.cu -- the FP64 product over several GPUs of one machine, behind the C ABI (ozb_mg_*, ozb_dgemm_mg).
+//
+// The reference is single-GPU (no NCCL, MPI, peer copy or cudaSetDevice anywhere in it); this is the one distributed
+// strategy that does not change a bit of the result. Rank g owns a block of rows of A and produces the same rows of C
+// (the reference's entry point python/capi.cu:77-89, with a row count per rank). Row scales belong to those rows; column
+// scales and residues of B are formed identically on every rank, so the only exchange is one broadcast of B from the rank
+// that holds it: ncclBroadcast over NVLink / NVSwitch on a communication stream of the library's own. Nothing else is
+// exchanged, no kernel of the library reads another GPU's memory, and B is in the GPU's own HBM before any kernel or TMA
+// load touches it.
+//
+// How B travels depends on its size:
+//   whole   (B up to 1 GiB) one transfer straight out of the holder's matrix, beside the residues of A; then the column
+//           maxima, the residues of B, the GEMMs and the reconstruction, each once at full width.
+//   stream  (larger B) the holder first reduces the column maxima of its B (one pass at HBM speed) and sends those 8 N
+//           bytes ahead; B follows in pieces of whole rows (contiguous, nothing is packed). Every rank turns a piece into
+//           residues the moment it has landed and, as soon as the pieces of a K range of about 8192 are there, runs the
+//           INT8 GEMMs of that range at full width, adding to the residues of the ranges before it (the same cut of a
+//           long K the single-GPU product makes to keep its panels in L2). The reconstruction runs once at the end.
+//
+// NCCL is loaded at run time (dlopen of libnccl.so.2: the library itself links against nothing but the driver), the
+// communicator is non-blocking, and every host-side wait is bounded: when a call does not settle or a product does not
+// finish within the handle's time budget -- a peer that never joined -- the communicator is aborted (ncclCommAbort), the
+// handle is marked broken and the call returns OZB_ECOMM; the CUDA context stays usable.
+#include <nccl.h>
+#include <dlfcn.h>
+#include <chrono>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <thread>
+#include "../../include/ozb.h"
+#include "oz_common.cuh"
+#include "oz_kernels.h"
+#include "oz_plan.h"
+
+#define OZB_API extern "C" __attribute__((visibility("default")))
+using namespace ozk;
+
+namespace {
+
+// ---------------------------------------------------------------------------------------------------------------
+// NCCL, loaded on first use
+// ---------------------------------------------------------------------------------------------------------------
+struct Nccl {
+    void *handle = nullptr;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
+    ncclResult_t (*CommInitRankConfig)(ncclComm_t *, int, ncclUniqueId, int, ncclConfig_t *) = nullptr;
+    ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t *) = nullptr;
+    ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*Broadcast)(const void *, void *, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*GroupStart)() = nullptr;
+    ncclResult_t (*GroupEnd)() = nullptr;
+    bool ok = false;
+};
+const Nccl &nccl() {
+    static Nccl n = [] {
+        Nccl n;
+        // a process that already holds NCCL (a framework's bundled copy) gets that one back: dlopen matches the soname
+        const char *env = getenv("OZB_NCCL_LIBRARY");
+        n.handle = dlopen(env && *env ? env : "libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+        if (!n.handle) return n;
+        auto sym = [&](const char *name) { return dlsym(n.handle, name); };
+        n.GetUniqueId = (decltype(n.GetUniqueId))sym("ncclGetUniqueId");
+        n.CommInitRankConfig = (decltype(n.CommInitRankConfig))sym("ncclCommInitRankConfig");
+        n.CommGetAsyncError = (decltype(n.CommGetAsyncError))sym("ncclCommGetAsyncError");
+        n.CommAbort = (decltype(n.CommAbort))sym("ncclCommAbort");
+        n.CommDestroy = (decltype(n.CommDestroy))sym("ncclCommDestroy");
+        n.Broadcast = (decltype(n.Broadcast))sym("ncclBroadcast");
+        n.GroupStart = (decltype(n.GroupStart))sym("ncclGroupStart");
+        n.GroupEnd = (decltype(n.GroupEnd))sym("ncclGroupEnd");
+        n.ok = n.GetUniqueId && n.CommInitRankConfig && n.CommGetAsyncError && n.CommAbort && n.CommDestroy && n.Broadcast && n.GroupStart &&
+               n.GroupEnd;
+        return n;
+    }();
+    return n;
+}
+
+using Clock = std::chrono::steady_clock;
+double ms_since(Clock::time_point t0) { return std::chrono::duration<double, std::milli>(Clock::now() - t0).count(); }
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------------------------
+// the handle: one per rank (process or thread) and device
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int MG_MAX_PIECES = 64, MG_MAX_BLOCKS = 32;
+struct ozb_mg {
+    int world, rank, dev, timeout_ms;
+    ncclComm_t comm;
+    bool broken;                       // the communicator was aborted: every later call answers OZB_ECOMM
+    cudaStream_t sComm, sIn, sRun, sOut;
+    cudaEvent_t evStart, evDone, evPiece[MG_MAX_PIECES], evIn[MG_MAX_PIECES], evRun[MG_MAX_BLOCKS];
+    ozb_plan *plan;
+    double *stageB; size_t stageB_elems;   // this rank's copy of B (receivers; a holder whose B is strided or comes from the host)
+    double *dA, *dC; size_t dA_elems, dC_elems;   // host-operand and single-process paths: this rank's rows on its device
+    int last_layout, last_pieces;      // what the last product did (0 whole, 1 stream), for reports
+};
+
+namespace {
+
+void mg_abort(ozb_mg *g) {
+    if (g->comm && !g->broken) nccl().CommAbort(g->comm);
+    g->comm = nullptr;
+    g->broken = true;
+}
+// waits, within the handle's budget, until the communicator has settled the call that returned `r`
+int mg_settle(ozb_mg *g, ncclResult_t r) {
+    const auto t0 = Clock::now();
+    while (r == ncclInProgress) {
+        if (ms_since(t0) > g->timeout_ms) { mg_abort(g); return OZB_ECOMM; }
+        std::this_thread::sleep_for(std::chrono::microseconds(20));
+        if (nccl().CommGetAsyncError(g->comm, &r) != ncclSuccess) { mg_abort(g); return OZB_ECOMM; }
+    }
+    if (r != ncclSuccess) { mg_abort(g); return OZB_ECOMM; }
+    return 0;
+}
+int mg_bcast(ozb_mg *g, void *buf, size_t bytes, int root) {
+    if (g->world == 1) return 0;   // a single rank holds B already; the rest of the schedule is the same
+    if (g->broken) return OZB_ECOMM;
+    return mg_settle(g, nccl().Broadcast(buf, buf, bytes, ncclChar, root, g->comm, g->sComm));
+}
+// waits for an event on the host, within the budget, watching the communicator: a product whose broadcast never completes
+// (a peer is gone) ends here with the communicator aborted instead of blocking in a synchronise call for ever
+void drain(cudaEvent_t ev, int budget_ms) {   // after an abort the collective's kernel leaves and the stream drains; bounded all the same
+    const auto t0 = Clock::now();
+    while (cudaEventQuery(ev) == cudaErrorNotReady && ms_since(t0) < budget_ms) std::this_thread::sleep_for(std::chrono::microseconds(200));
+}
+int mg_wait_event(ozb_mg *g, cudaEvent_t ev) {
+    const auto t0 = Clock::now();
+    for (unsigned spin = 0;; spin++) {
+        const cudaError_t q = cudaEventQuery(ev);
+        if (q == cudaSuccess) return 0;
+        if (q != cudaErrorNotReady) return (int)q;
+        if ((spin & 63) == 63 && g->comm) {
+            ncclResult_t r = ncclSuccess;
+            if (nccl().CommGetAsyncError(g->comm, &r) != ncclSuccess || (r != ncclSuccess && r != ncclInProgress)) {
+                mg_abort(g);
+                drain(ev, g->timeout_ms);
+                return OZB_ECOMM;
+            }
+        }
+        if (ms_since(t0) > g->timeout_ms) {
+            if (g->world > 1) mg_abort(g);
+            drain(ev, g->timeout_ms);
+            return g->world > 1 ? OZB_ECOMM : OZB_ETIMEOUT;
+        }
+        if (spin > 2000) std::this_thread::sleep_for(std::chrono::microseconds(50));
+    }
+}
+
+cudaError_t grow(double **buf, size_t *have, size_t want) {
+    if (*have >= want) return cudaSuccess;
+    cudaFree(*buf);
+    *buf = nullptr; *have = 0;
+    cudaError_t e = cudaMalloc(buf, want * sizeof(double));
+    if (e) { cudaGetLastError(); return e; }
+    *have = want;
+    return cudaSuccess;
+}
+int mg_plan(ozb_mg *g, int m, int N, int K, int nm) {
+    ozb_plan *p = g->plan;
+    if (p && (p->M != m || p->N != N || p->K != K || p->nm != nm)) { ozb_plan_free_internal(p); g->plan = nullptr; }
+    if (!g->plan) if (int e = ozb_plan_make_internal(m, N, K, nm, 62, &g->plan)) { g->plan = nullptr; return e; }
+    return 0;
+}
+
+// rows per piece of a K x N matrix sent in pieces of about `target` bytes: a multiple of 128 rows, at most MG_MAX_PIECES pieces
+int piece_rows(int K, int N, size_t target) {
+    long long rows = (long long)(target / ((size_t)N * 8)) / 128 * 128;
+    if (rows < 128) rows = 128;
+    while ((K + rows - 1) / rows > MG_MAX_PIECES) rows += 128;
+    return (int)rows;
+}
+
+enum { LAYOUT_WHOLE = 0, LAYOUT_STREAM = 1 };
+int choose_layout(int K, int N) {
+    static const int forced = [] {
+        const char *env = getenv("OZ_MG_LAYOUT");
+        return !env ? -1 : !strcmp(env, "whole") ? LAYOUT_WHOLE : !strcmp(env, "stream") ? LAYOUT_STREAM : -1;
+    }();
+    if (forced >= 0) return forced;
+    return (size_t)K * N * 8 <= ((size_t)1 << 30) ? LAYOUT_WHOLE : LAYOUT_STREAM;
+}
+
+// C_local = A_local B on device operands; B is read on `root` only. Asynchronous on `st` (and the handle's own
+// communication stream); ozb_mg_wait reports how it ended.
+int mg_dgemm_dev(ozb_mg *g, int m, int N, int K, const double *A, long long lda, const double *B, long long ldb, double *C,
+                 long long ldc, int nm, int root, cudaStream_t st) {
+    if (g->broken) return OZB_ECOMM;
+    if (int e = mg_plan(g, m, N, K, nm)) return e;
+    ozb_plan *p = g->plan;
+    p->last = st;
+    cudaError_t e = cudaSuccess;
+    const bool src = g->rank == root;
+    const bool in_place = src && ldb == N;            // a dense B is sent from where it lies
+    if (!in_place) if ((e = grow(&g->stageB, &g->stageB_elems, (size_t)K * N))) return (int)e;
+    double *whole = in_place ? const_cast<double *>(B) : g->stageB;
+    const int layout = choose_layout(K, N);
+    // order: after the caller's writes of A and B (stream st), and after the previous product's reads of the staging copy
+    if (src && !in_place) e = cudaMemcpy2DAsync(g->stageB, (size_t)N * 8, B, (size_t)ldb * 8, (size_t)N * 8, K, cudaMemcpyDeviceToDevice, st);
+    if (!e) e = cudaMemsetAsync(p->colmax, 0, (size_t)N * 8, st);
+    if (!e && layout == LAYOUT_STREAM && src) e = cols_absmax_accumulate(whole, K, N, N, p->colmax, st);
+    if (!e) e = cudaEventRecord(g->evStart, st);
+    if (!e) e = cudaStreamWaitEvent(g->sComm, g->evStart, 0);
+    if (!e) e = cudaStreamWaitEvent(g->sComm, g->evDone, 0);
+    if (e) return (int)e;
+
+    int rows = K, pieces = 1;
+    if (layout == LAYOUT_STREAM) {
+        static const size_t target = [] { const char *env = getenv("OZ_MG_PIECE_MB"); const int v = env && *env ? atoi(env) : 0; return (size_t)(v > 0 ? v : 512) << 20; }();
+        rows = piece_rows(K, N, target);
+        pieces = (K + rows - 1) / rows;
+        if (int c = mg_bcast(g, p->colmax, (size_t)N * 8, root)) return c;   // the column maxima, ahead of B
+    }
+    for (int i = 0; i < pieces; i++) {
+        const int k0 = i * rows, len = K - k0 < rows ? K - k0 : rows;
+        if (int c = mg_bcast(g, whole + (size_t)k0 * N, (size_t)len * N * 8, root)) return c;
+        if ((e = cudaEventRecord(g->evPiece[i], g->sComm))) return (int)e;
+    }
+    g->last_layout = layout; g->last_pieces = pieces;
+
+    // compute stream: the residues of A run beside the first transfer
+    e = scale_residues_rows(nm, A, m, K, lda, p->bits, p->sa, p->Ar, p->Kp, p->planeA, st);
+    if (layout == LAYOUT_WHOLE) {
+        if (!e && !src) e = cudaStreamWaitEvent(st, g->evPiece[0], 0);
+        if (!e) e = cols_absmax_accumulate(whole, K, N, N, p->colmax, st);
+        if (!e) e = cols_residues_from_max(nm, whole, K, N, N, p->bits, p->colmax, p->sb, p->Br, p->Kp, p->planeB, st);
+        if (!e) e = ozb_plan_gemm_range(p, N, 0, K, 0, st);
+    } else {
+        // K ranges of the GEMMs: a first short one (the product starts early), then about 8192 each, on piece boundaries
+        static const int kchunk = [] { const char *env = getenv("OZ_KCHUNK"); const int v = env && *env ? atoi(env) : 0; return v >= 1024 ? v : 8192; }();
+        int done = 0, range_k0 = 0, ranges = 0;
+        if (!src) e = cudaStreamWaitEvent(st, g->evPiece[0], 0);   // the maxima were sent before the first piece on the same stream
+        for (int i = 0; i < pieces && !e; i++) {
+            const int k0 = i * rows, len = K - k0 < rows ? K - k0 : rows;
+            if (!src && i > 0) e = cudaStreamWaitEvent(st, g->evPiece[i], 0);
+            if (!e) e = cols_residues_from_max(nm, whole + (size_t)k0 * N, len, N, N, p->bits, p->colmax, p->sb, p->Br + k0, p->Kp, p->planeB, st);
+            done = k0 + len;
+            const int want = ranges == 0 ? kchunk / 2 : kchunk;
+            const bool last = i == pieces - 1;
+            // close the range when it is long enough, unless what would remain is too short to be a range of its own
+            if (!e && (last || (done - range_k0 >= want && K - done >= kchunk / 4))) {
+                e = ozb_plan_gemm_range(p, N, range_k0, done - range_k0, ranges > 0, st);
+                range_k0 = done; ranges++;
+            }
+        }
+    }
+    if (!e) e = crt_from_i8(nm, p->Cr, p->planeC, m, N, p->Np, p->sa, p->sb, C, ldc, st);
+    // the holder's stream also waits for the sends: the caller may overwrite B (or the next call the staging copy) after this call
+    if (!e && src) e = cudaStreamWaitEvent(st, g->evPiece[pieces - 1], 0);
+    if (!e) e = cudaEventRecord(g->evDone, st);
+    return (int)e;
+}
+
+// The same product on host operands (pinned memory makes the copies asynchronous): B goes to the holder's GPU in pieces
+// of rows, each piece is broadcast as it lands and its column maxima are taken on every rank as it arrives; once B is
+// complete its residues are formed, while this rank's rows of A follow in blocks. A block of rows of C needs only its
+// rows of A, so each block is scaled, multiplied and reconstructed as soon as it has landed and travels back while the
+// next one is in flight (the block pipeline of the single-GPU host path). Synchronous.
+int mg_dgemm_host(ozb_mg *g, int m, int N, int K, const double *A, const double *B, double *C, int nm, int root) {
+    if (g->broken) return OZB_ECOMM;
+    if (int e = mg_plan(g, m, N, K, nm)) return e;
+    ozb_plan *p = g->plan;
+    cudaError_t e = grow(&g->stageB, &g->stageB_elems, (size_t)K * N);
+    if (!e) e = grow(&g->dA, &g->dA_elems, (size_t)m * K);
+    if (!e) e = grow(&g->dC, &g->dC_elems, (size_t)m * N);
+    if (e) return (int)e;
+    const bool src = g->rank == root;
+    p->last = g->sRun;
+    int pieces = K / 512;
+    if (pieces > 16) pieces = 16;
+    if (pieces < 1) pieces = 1;
+    const int rows = (K + pieces - 1) / pieces;
+    pieces = (K + rows - 1) / rows;
+    e = cudaMemsetAsync(p->colmax, 0, (size_t)N * 8, g->sRun);
+    for (int i = 0; i < pieces && !e; i++) {
+        const size_t k0 = (size_t)i * rows;
+        const int len = (int)(K - k0 < (size_t)rows ? K - k0 : rows);
+        if (src) {
+            e = cudaMemcpyAsync(g->stageB + k0 * N, B + k0 * N, (size_t)len * N * 8, cudaMemcpyHostToDevice, g->sIn);
+            if (!e) e = cudaEventRecord(g->evIn[i], g->sIn);
+            if (!e) e = cudaStreamWaitEvent(g->sComm, g->evIn[i], 0);
+        }
+        if (e) break;
+        if (g->world > 1) {
+            if (int c = mg_bcast(g, g->stageB + k0 * N, (size_t)len * N * 8, root)) return c;
+            e = cudaEventRecord(g->evPiece[i], g->sComm);
+            if (!e) e = cudaStreamWaitEvent(g->sRun, g->evPiece[i], 0);
+        } else {
+            e = cudaStreamWaitEvent(g->sRun, g->evIn[i], 0);
+        }
+        if (!e) e = cols_absmax_accumulate(g->stageB + k0 * N, len, N, N, p->colmax, g->sRun);
+    }
+    if (!e) e = cols_residues_from_max(nm, g->stageB, K, N, N, p->bits, p->colmax, p->sb, p->Br, p->Kp, p->planeB, g->sRun);
+    int blocks = m / 512;
+    if (blocks > 16) blocks = 16;
+    if (blocks < 1) blocks = 1;
+    const int mblock = (m + blocks - 1) / blocks;
+    size_t i0 = 0;
+    for (int q = 0; i0 < (size_t)m && !e; q++) {   // the last blocks are halved down to 128 rows: what follows the last copy is exposed
+        const size_t left = m - i0;
+        size_t m_ = left > (size_t)mblock ? (size_t)mblock : (left > 128 ? (left / 2 + 127) / 128 * 128 : left);
+        if (q >= MG_MAX_BLOCKS - 1 || m_ > left) m_ = left;
+        const int mb = (int)m_;
+        static_assert(16 + MG_MAX_BLOCKS <= MG_MAX_PIECES, "evIn holds the pieces of B and the blocks of A");
+        e = cudaMemcpyAsync(g->dA + i0 * K, A + i0 * K, (size_t)mb * K * 8, cudaMemcpyHostToDevice, g->sIn);
+        if (!e) e = cudaEventRecord(g->evIn[pieces + q], g->sIn);
+        if (!e) e = cudaStreamWaitEvent(g->sRun, g->evIn[pieces + q], 0);
+        if (!e) e = scale_residues_rows(nm, g->dA + i0 * K, mb, K, K, p->bits, p->sa + i0, p->Ar + i0 * p->Kp, p->Kp, p->planeA, g->sRun);
+        if (!e) e = ozb_plan_gemm_range(p, N, 0, K, 0, g->sRun, (int)i0, mb);
+        if (!e) e = crt_from_i8(nm, p->Cr + i0 * p->Np, p->planeC, mb, N, p->Np, p->sa + i0, p->sb, g->dC + i0 * N, N, g->sRun);
+        if (!e) e = cudaEventRecord(g->evRun[q], g->sRun);
+        if (!e) e = cudaStreamWaitEvent(g->sOut, g->evRun[q], 0);
+        if (!e) e = cudaMemcpyAsync(C + i0 * N, g->dC + i0 * N, (size_t)mb * N * 8, cudaMemcpyDeviceToHost, g->sOut);
+        i0 += m_;
+    }
+    if (e) return (int)e;
+    if ((e = cudaEventRecord(g->evDone, g->sOut))) return (int)e;
+    if (int c = mg_wait_event(g, g->evDone)) return c;
+    if ((e = cudaStreamSynchronize(g->sRun))) return (int)e;
+    if ((e = cudaStreamSynchronize(g->sIn))) return (int)e;
+    if (g->world > 1 && !g->broken) if ((e = cudaStreamSynchronize(g->sComm))) return (int)e;
+    g->last_layout = LAYOUT_WHOLE; g->last_pieces = pieces;
+    return ozb_read_status_words(p->status);
+}
+
+int check_device() {
+    int dev, major;
+    if (cudaGetDevice(&dev) || cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev)) return (int)cudaGetLastError();
+    return major != 10 ? OZB_EARCH : 0;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------------------------
+// C ABI
+// ---------------------------------------------------------------------------------------------------------------
+OZB_API int ozb_mg_unique_id(void *id) {
+    if (!id) return OZB_EARG;
+    if (!nccl().ok) return OZB_ENCCL;
+    static_assert(sizeof(ncclUniqueId) == OZB_MG_ID_BYTES, "rendezvous id size");
+    ncclUniqueId u;
+    if (nccl().GetUniqueId(&u) != ncclSuccess) return OZB_ECOMM;
+    memcpy(id, &u, sizeof u);
+    return 0;
+}
+
+OZB_API int ozb_mg_create(int world, int rank, const void *id, int timeout_ms, ozb_mg **out) {
+    if (!out || world < 1 || rank < 0 || rank >= world || (world > 1 && !id) || timeout_ms < 0) return OZB_EARG;
+    if (int e = check_device()) return e;
+    if (world > 1 && !nccl().ok) return OZB_ENCCL;
+    ozb_mg *g = new ozb_mg();
+    memset(g, 0, sizeof *g);
+    g->world = world; g->rank = rank; g->timeout_ms = timeout_ms ? timeout_ms : 30000;
+    cudaGetDevice(&g->dev);
+    int lo = 0, hi = 0;
+    cudaError_t e = cudaDeviceGetStreamPriorityRange(&lo, &hi);
+    // the communication stream has the highest priority: a transfer kernel queued behind a compute kernel's block dispatch waits otherwise
+    if (!e) e = cudaStreamCreateWithPriority(&g->sComm, cudaStreamNonBlocking, hi);
+    if (!e) e = cudaStreamCreateWithFlags(&g->sIn, cudaStreamNonBlocking);
+    if (!e) e = cudaStreamCreateWithFlags(&g->sRun, cudaStreamNonBlocking);
+    if (!e) e = cudaStreamCreateWithFlags(&g->sOut, cudaStreamNonBlocking);
+    if (!e) e = cudaEventCreateWithFlags(&g->evStart, cudaEventDisableTiming);
+    if (!e) e = cudaEventCreateWithFlags(&g->evDone, cudaEventDisableTiming);
+    for (auto &ev : g->evPiece) if (!e) e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+    for (auto &ev : g->evIn) if (!e) e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+    for (auto &ev : g->evRun) if (!e) e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+    int rc = (int)e;
+    if (!rc && world > 1) {
+        ncclUniqueId u;
+        memcpy(&u, id, sizeof u);
+        ncclConfig_t cfg = NCCL_CONFIG_INITIALIZER;
+        cfg.blocking = 0;
+        const char *env = getenv("OZ_MG_MAX_CTAS");   // SMs NCCL's kernels may hold while they run beside the GEMMs
+        if (env && atoi(env) > 0) cfg.maxCTAs = atoi(env);
+        rc = mg_settle(g, nccl().CommInitRankConfig(&g->comm, world, u, rank, &cfg));
+        if (!rc) {   // initialisation itself proceeds in the background: wait for it within the budget
+            ncclResult_t r = ncclInProgress;
+            if (nccl().CommGetAsyncError(g->comm, &r) != ncclSuccess) r = ncclInternalError;
+            rc = mg_settle(g, r);
+        }
+    }
+    if (rc) { ozb_mg_destroy(g); return rc; }
+    *out = g;
+    return 0;
+}
+
+OZB_API void ozb_mg_destroy(ozb_mg *g) {
+    if (!g) return;
+    int cur = -1;
+    const int dev = g->dev;
+    cudaGetDevice(&cur);
+    if (cur != dev) cudaSetDevice(dev);
+    if (g->comm && !g->broken) {
+        cudaStreamSynchronize(g->sComm);
+        nccl().CommDestroy(g->comm);
+    }
+    if (g->plan) ozb_plan_free_internal(g->plan);
+    cudaFree(g->stageB); cudaFree(g->dA); cudaFree(g->dC);
+    for (cudaStream_t s : {g->sComm, g->sIn, g->sRun, g->sOut}) if (s) cudaStreamDestroy(s);
+    for (cudaEvent_t ev : {g->evStart, g->evDone}) if (ev) cudaEventDestroy(ev);
+    for (auto ev : g->evPiece) if (ev) cudaEventDestroy(ev);
+    for (auto ev : g->evIn) if (ev) cudaEventDestroy(ev);
+    for (auto ev : g->evRun) if (ev) cudaEventDestroy(ev);
+    delete g;
+    if (cur >= 0 && cur != dev) cudaSetDevice(cur);
+}
+
+OZB_API int ozb_mg_dgemm(ozb_mg *g, int m_local, int N, int K, const double *A, long long lda, const double *B, long long ldb, double *C,
+                         long long ldc, int moduli, int root, int on_host, void *stream) {
+    if (!g || m_local <= 0 || N <= 0 || K <= 0 || moduli < 8 || moduli > 16 || root < 0 || root >= g->world || !A || !C) return OZB_EARG;
+    if (K >= 131072) return OZB_EK;
+    if (g->rank == root && !B) return OZB_EARG;
+    int dev = -1;
+    if (cudaGetDevice(&dev) || dev != g->dev) return (int)cudaErrorInvalidDevice;
+    if (on_host) {
+        if (lda != K || ldc != N || (g->rank == root && ldb != N)) return OZB_EARG;   // host operands are dense, as in ozb_dgemm
+        return mg_dgemm_host(g, m_local, N, K, A, B, C, moduli, root);
+    }
+    if (lda < K || ldc < N || (g->rank == root && ldb < N)) return OZB_EARG;
+    return mg_dgemm_dev(g, m_local, N, K, A, lda, B, ldb, C, ldc, moduli, root, (cudaStream_t)stream);
+}
+
+OZB_API int ozb_mg_wait(ozb_mg *g) {
+    if (!g) return OZB_EARG;
+    if (g->broken) return OZB_ECOMM;
+    if (!g->plan) return 0;
+    if (int c = mg_wait_event(g, g->evDone)) return c;
+    return ozb_read_status_words(g->plan->status);
+}
+
+OZB_API int ozb_mg_info(ozb_mg *g, int *layout, int *pieces) {
+    if (!g) return OZB_EARG;
+    if (layout) *layout = g->last_layout;
+    if (pieces) *pieces = g->last_pieces;
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// one process, several devices: the reference's ozb_dgemm with a device count
+// ---------------------------------------------------------------------------------------------------------------
+namespace {
+std::mutex mg_mu;
+ozb_mg *mg_handles[16] = {};
+int mg_ndev = 0;
+
+void mg_release_all() {
+    for (int d = 0; d < mg_ndev; d++) { ozb_mg_destroy(mg_handles[d]); mg_handles[d] = nullptr; }
+    mg_ndev = 0;
+}
+void row_block(int M, int r, int world, int *lo, int *hi) {   // blocks differ by at most one row, earlier ranks get the longer ones
+    const int base = M / world, extra = M % world;
+    *lo = r * base + (r < extra ? r : extra);
+    *hi = *lo + base + (r < extra ? 1 : 0);
+}
+}  // namespace
+
+OZB_API int ozb_dgemm_mg(int M, int N, int K, const double *A, const double *B, double *C, int moduli, int on_host, int ndev) {
+    if (M <= 0 || N <= 0 || K <= 0 || moduli < 8 || moduli > 16 || ndev < 1 || ndev > 16 || !A || !B || !C) return OZB_EARG;
+    if (K >= 131072) return OZB_EK;
+    int have = 0, cur = 0;
+    if (cudaGetDeviceCount(&have) || cudaGetDevice(&cur)) return (int)cudaGetLastError();
+    if (ndev > have) return OZB_EARG;
+    if (ndev > M) ndev = M;
+    std::lock_guard<std::mutex> lock(mg_mu);
+    int rcs[16] = {};
+    if (mg_ndev != ndev) {   // one handle per device 0 .. ndev-1, made by one thread per device as separate processes would
+        mg_release_all();
+        char id[OZB_MG_ID_BYTES] = {};
+        if (ndev > 1) if (int e = ozb_mg_unique_id(id)) return e;
+        std::thread th[16];
+        for (int d = 0; d < ndev; d++)
+            th[d] = std::thread([&, d] { rcs[d] = (int)cudaSetDevice(d); if (!rcs[d]) rcs[d] = ozb_mg_create(ndev, d, id, 0, &mg_handles[d]); });
+        for (int d = 0; d < ndev; d++) th[d].join();
+        mg_ndev = ndev;
+        for (int d = 0; d < ndev; d++) if (rcs[d]) { const int e = rcs[d]; mg_release_all(); cudaSetDevice(cur); return e; }
+    }
+    // device operands live on the calling thread's current device, which also holds B: that device is the root and works
+    // in place, the others get their rows of A and return their rows of C with peer copies
+    const int root = on_host ? 0 : (cur < ndev ? cur : 0);
+    if (!on_host && cur >= ndev) return OZB_EARG;
+    if (!on_host) if (cudaError_t e = cudaDeviceSynchronize()) return (int)e;   // the operands' pending writes, whatever stream made them
+    std::thread th[16];
+    for (int d = 0; d < ndev; d++)
+        th[d] = std::thread([&, d] {
+            int &rc = rcs[d];
+            rc = (int)cudaSetDevice(d);
+            if (rc) return;
+            ozb_mg *g = mg_handles[d];
+            int lo, hi;
+            row_block(M, d, ndev, &lo, &hi);
+            const int m = hi - lo;
+            if (on_host) { rc = mg_dgemm_host(g, m, N, K, A + (size_t)lo * K, d == root ? B : nullptr, C + (size_t)lo * N, moduli, root); return; }
+            if (d == cur) {
+                rc = mg_dgemm_dev(g, m, N, K, A + (size_t)lo * K, K, B, N, C + (size_t)lo * N, N, moduli, root, g->sRun);
+            } else {
+                cudaError_t e = grow(&g->dA, &g->dA_elems, (size_t)m * K);
+                if (!e) e = grow(&g->dC, &g->dC_elems, (size_t)m * N);
+                if (!e) e = cudaMemcpyPeerAsync(g->dA, d, A + (size_t)lo * K, cur, (size_t)m * K * 8, g->sRun);
+                rc = (int)e;
+                if (!rc) rc = mg_dgemm_dev(g, m, N, K, g->dA, K, nullptr, N, g->dC, N, moduli, root, g->sRun);
+                if (!rc) rc = (int)cudaMemcpyPeerAsync(C + (size_t)lo * N, cur, g->dC, d, (size_t)m * N * 8, g->sRun);
+                if (!rc) rc = (int)cudaEventRecord(g->evDone, g->sRun);
+            }
+            if (!rc) rc = ozb_mg_wait(g);
+        });
+    for (int d = 0; d < ndev; d++) th[d].join();
+    cudaSetDevice(cur);
+    int rc = 0;
+    for (int d = 0; d < ndev; d++) if (rcs[d] && !rc) rc = rcs[d];
+    if (rc == OZB_ECOMM) mg_release_all();   // an aborted communicator cannot be used again: the next call starts afresh
+    return rc;
+}
+
+OZB_API void ozb_mg_release(void) {
+    std::lock_guard<std::mutex> lock(mg_mu);
+    mg_release_all();
+}

@@ -40,6 +40,18 @@ template <int L>
 __device__ __forceinline__ uint32_t mod_magic(uint32_t u) {
     return u - __umulhi(u, magic_of(L)) * (uint32_t)modulus(L);
 }
+// Balanced residue in one step less: `a` is a non-negative representative of the class that is already shifted down by
+// floor(m/2), i.e. a = S + (multiple of m) with S the signed sum. Then bal(S) = a - floor((a + floor(m/2)) / m) * m, and the
+// quotient is the high word of a * magic + floor(m/2) * magic: one wide multiply-add with a constant addend, one
+// multiply-add. Exact while a + floor(m/2) is below the bound checked by magic_ok(). Returns the residue as a 32-bit
+// two's-complement value (its low byte is the int8).
+template <int L>
+__device__ __forceinline__ uint32_t balanced_magic(uint32_t a) {
+    constexpr unsigned long long add = (unsigned long long)half_of(L) * magic_of(L);
+    unsigned long long prod;
+    asm("mad.wide.u32 %0, %1, %2, %3;" : "=l"(prod) : "r"(a), "r"(magic_of(L)), "l"(add));
+    return a - (uint32_t)(prod >> 32) * (uint32_t)modulus(L);
+}
 // 2^s as a double for -1022 <= s <= 1023
 __device__ __forceinline__ double pow2_normal(int s) { return __hiloint2double((s + 1023) << 20, 0); }
 // llrint(ldexp(x, s)) as the reference computes it (src/ozaki2.cuh:76). For s in the normal exponent range the scaling

@@ -34,14 +34,13 @@ __device__ __forceinline__ void residues_of_4(const long long (&v)[4], Put &&put
         constexpr int l = decltype(L)::value, m = modulus(l);
         constexpr uint32_t wlo = pack4(byte_weight(0, l), byte_weight(1, l), byte_weight(2, l), byte_weight(3, l));
         constexpr uint32_t whi = pack4(byte_weight(4, l), byte_weight(5, l), byte_weight(6, l), byte_weight(7, l));
-        constexpr int init = lift_of(l, BYTES_BOUND) - pow2_mod(62, m);
-        static_assert(init > BYTES_BOUND && magic_ok(l, (uint64_t)init + BYTES_BOUND), "multiply-high reduction out of range");
+        // a multiple of m that lifts the byte sum above zero, minus 2^62 mod m (the offset added above); the +floor(m/2)
+        // that balances the residue is folded into the quotient (balanced_magic)
+        constexpr int init = lift_of(l, BYTES_BOUND) - half_of(l) - pow2_mod(62, m);
+        static_assert(init > BYTES_BOUND && magic_ok(l, (uint64_t)init + half_of(l) + BYTES_BOUND), "multiply-high reduction out of range");
         uint32_t x[4];
 #pragma unroll
-        for (int e = 0; e < 4; e++) {
-            const uint32_t u = (uint32_t)dp4a_us(hi[e], whi, dp4a_us(lo[e], wlo, init));
-            x[e] = mod_magic<l>(u) - (uint32_t)half_of(l);
-        }
+        for (int e = 0; e < 4; e++) x[e] = balanced_magic<l>((uint32_t)dp4a_us(hi[e], whi, dp4a_us(lo[e], wlo, init)));
         put(L, pack_low_bytes(x[0], x[1], x[2], x[3]));
     });
 }

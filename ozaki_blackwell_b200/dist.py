@@ -164,6 +164,48 @@ class CudaEngine:
             self._plan = ctypes.c_void_p()
 
 
+class NativeSharded:
+    """The same product through the library's own multi-GPU layer (ozb_mg_*: NCCL driven from C++, non-blocking
+    communicator, bounded host waits). One handle per rank; the rendezvous id travels over the process group."""
+
+    def __init__(self, moduli, group=None, src=0, timeout_ms=0):
+        from ._lib import lib
+        self._lib, self.moduli, self.src = lib, moduli, src
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        ident = ctypes.create_string_buffer(128)
+        if rank == 0:
+            self._check(lib.ozb_mg_unique_id(ident))
+        box = [ident.raw]
+        dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+        self._handle = ctypes.c_void_p()
+        self._check(lib.ozb_mg_create(world, rank, box[0], timeout_ms, ctypes.byref(self._handle)))
+
+    def _check(self, code):
+        if code:
+            raise RuntimeError(self._lib.ozb_error(code).decode())
+
+    def __call__(self, a_local, b, c_local, stream, on_host=False):
+        m, k = a_local.shape
+        n = c_local.shape[1]
+        b_ptr, ldb = (b.data_ptr(), b.stride(0)) if b is not None else (None, n)
+        self._check(self._lib.ozb_mg_dgemm(self._handle, m, n, k, a_local.data_ptr(), a_local.stride(0), b_ptr, ldb, c_local.data_ptr(),
+                                           c_local.stride(0), self.moduli, self.src, 1 if on_host else 0,
+                                           None if on_host else stream.cuda_stream))
+
+    def status(self):
+        self._check(self._lib.ozb_mg_wait(self._handle))
+
+    def info(self):
+        layout, pieces = ctypes.c_int(), ctypes.c_int()
+        self._check(self._lib.ozb_mg_info(self._handle, ctypes.byref(layout), ctypes.byref(pieces)))
+        return ("whole", "stream")[layout.value], pieces.value
+
+    def close(self):
+        if self._handle:
+            self._lib.ozb_mg_destroy(self._handle)
+            self._handle = ctypes.c_void_p()
+
+
 class _HostStreams:
     """Stand-ins for CUDA streams and events on CPU ranks (gloo tests): everything is synchronous there."""
 
@@ -195,14 +237,24 @@ class RowShardedGemm:
     (row chunks for layout "rows", column panels for layout "panels"); both default to a choice by the size of B.
     """
 
-    def __init__(self, m_local, n, k, moduli=16, group=None, src=0, panels=None, engine=None, device=None, layout="auto"):
+    def __init__(self, m_local, n, k, moduli=16, group=None, src=0, panels=None, engine=None, device=None, layout="auto",
+                 native=None, timeout_ms=0):
         if layout not in ("auto", "rows", "panels"):
             raise ValueError("layout is 'auto', 'rows' or 'panels'")
-        layout, panels = choose_layout(k, n, layout, panels)
-        self.group, self.src, self.layout = group, src, layout
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.m, self.n, self.k, self.moduli = m_local, n, k, moduli
+        # On GPUs the exchange is driven by the library itself unless a layout of this module is asked for by name; the
+        # orchestration below is the same strategy written against torch.distributed (any backend; gloo in the CPU tests).
+        if native is None:
+            native = engine is None and self.world > 1 and layout == "auto" and panels is None
+        self.native = NativeSharded(moduli, group, src, timeout_ms) if native else None
+        if self.native:
+            self.group, self.src, self.layout, self.ranges = group, src, "native", [(0, k)]
+            self.engine, self.compute, self.stage = self.native, torch.cuda.current_stream(), None
+            return
+        layout, panels = choose_layout(k, n, layout, panels)
+        self.group, self.src, self.layout = group, src, layout
         pieces = panels if self.world > 1 else 1
         if layout == "rows":
             self.ranges = row_chunks(k, pieces)
@@ -229,6 +281,14 @@ class RowShardedGemm:
 
     def __call__(self, a_local, b, c_local):
         """a_local [m_local, k], c_local [m_local, n]; b [k, n] is read on rank `src` only (others may pass None)."""
+        if self.native:
+            if self.rank == self.src and b.stride(1) != 1:
+                b = b.contiguous()
+            self.native(a_local, b if self.rank == self.src else None, c_local, torch.cuda.current_stream())
+            if self.layout == "native":
+                self.layout, pieces = self.native.info()
+                self.ranges = [(0, self.k)] * pieces
+            return c_local
         if self.world == 1:
             self.engine.full(a_local, b, c_local, self.compute)
             return c_local
@@ -338,6 +398,14 @@ class RowShardedGemm:
         if in_place:
             self.compute.wait_stream(self.comm)
         return c_local
+
+    def host(self, a_host, b_host, c_host):
+        """The product on host operands (pinned memory), copies pipelined with the broadcast and the computation inside the
+        library; synchronous. Native path only."""
+        if not self.native:
+            raise RuntimeError("host operands go through the library's own multi-GPU layer")
+        self.native(a_host, b_host if self.rank == self.src else None, c_host, None, on_host=True)
+        return c_host
 
     def close(self):
         close = getattr(self.engine, "close", None)

@@ -20,6 +20,11 @@ static int dp4a(uint32_t a, uint32_t b, int c, bool a_signed) {
     return c;
 }
 static uint32_t umulhi(uint32_t a, uint32_t b) { return (uint32_t)(((uint64_t)a * b) >> 32); }
+// oz_common.cuh: balanced_magic<L> -- the quotient of (a + floor(m/2)) / m from one wide multiply-add with a constant addend
+template <int L> static uint32_t balanced_magic(uint32_t a) {
+    const uint64_t prod = (uint64_t)a * magic_of(L) + (uint64_t)half_of(L) * magic_of(L);
+    return a - (uint32_t)(prod >> 32) * (uint32_t)modulus(L);
+}
 static int bal(long long x, int m) { return bal_c(x, m); }
 
 template <int L> struct PerMod {
@@ -28,11 +33,11 @@ template <int L> struct PerMod {
         if (l == 0) return (int)(int8_t)(v & 255);
         constexpr uint32_t wlo = pack4(byte_weight(0, l), byte_weight(1, l), byte_weight(2, l), byte_weight(3, l));
         constexpr uint32_t whi = pack4(byte_weight(4, l), byte_weight(5, l), byte_weight(6, l), byte_weight(7, l));
-        constexpr int init = lift_of(l, BYTES_BOUND) - pow2_mod(62, m);
-        static_assert(init > BYTES_BOUND && magic_ok(l, (uint64_t)init + BYTES_BOUND), "range");
+        constexpr int init = lift_of(l, BYTES_BOUND) - half_of(l) - pow2_mod(62, m);
+        static_assert(init > BYTES_BOUND && magic_ok(l, (uint64_t)init + half_of(l) + BYTES_BOUND), "range");
         const uint64_t w = (uint64_t)v + (1ull << 62);
         const uint32_t u = (uint32_t)dp4a((uint32_t)(w >> 32), whi, dp4a((uint32_t)w, wlo, init, false), false);
-        return (int)(int8_t)((u - umulhi(u, magic_of(l)) * (uint32_t)m - (uint32_t)half_of(l)) & 255);
+        return (int)(int8_t)(balanced_magic<l>(u) & 255);
     }
     static int residue_of_product(int32_t x) {
         constexpr ModConsts mc = mod_consts(L);
@@ -48,14 +53,14 @@ template <int NM> static void garner_fast(const int *r, int *x) {   // r: balanc
     x[0] = (int)(int8_t)(X[0] & 255);
     static_for<1, NM>([&](auto Lc) {
         constexpr int l = decltype(Lc)::value, m = modulus(l);
-        int acc = lift_of(l, GARNER_BOUND);
+        int acc = lift_of(l, GARNER_BOUND) - half_of(l);
         for (int g = 0; g <= l / 4; g++) {
             int c[4];
             for (int q = 0; q < 4; q++) { const int idx = 4 * g + q; c[q] = idx < l ? garner_q(idx, l) : (idx == l ? garner_p(l) : 0); }
             acc = dp4a(X[g], pack4(c[0], c[1], c[2], c[3]), acc, true);
         }
-        const uint32_t rr = (uint32_t)acc - umulhi((uint32_t)acc, magic_of(l)) * (uint32_t)m;
-        const int xl = (int)rr - half_of(l);
+        const int xl = (int)balanced_magic<l>((uint32_t)acc);
+        (void)m;
         X[l / 4] = (X[l / 4] & ~(255u << (8 * (l % 4)))) | ((uint32_t)(xl & 255) << (8 * (l % 4)));
         x[l] = xl;
     });

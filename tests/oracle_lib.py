@@ -22,6 +22,7 @@ def _load():
     lib = ctypes.CDLL(_SO)
     i, ll, d, p, sz = ctypes.c_int, ctypes.c_longlong, ctypes.c_double, ctypes.c_void_p, ctypes.c_size_t
     lib.oz_oracle_modulus.argtypes = [i]
+    lib.oz_oracle_set_threads.argtypes = [i]
     lib.oz_oracle_inv_mod.argtypes = [i, i]
     lib.oz_oracle_bits_for.argtypes = [i, i, i]
     lib.oz_oracle_scales.argtypes = [p, i, i, ll, ll, i, p]
@@ -51,6 +52,11 @@ lib = _load()
 
 def _ptr(a):
     return a.ctypes.data
+
+
+def set_threads(n=0):
+    """OpenMP threads of the checker (n = 0: only report). Needed under launchers that export OMP_NUM_THREADS=1."""
+    return lib.oz_oracle_set_threads(n)
 
 
 def modulus(l):
