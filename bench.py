@@ -582,18 +582,14 @@ class Bench:
             h2d, d2h = (M * K + K * N) * 8, M * N * 8
             how = "ozb_dgemm(on_host=1): the reference's entry point, pinned host operands, block-pipelined copies inside"
         else:
-            Ad = torch.empty_like(A)
-            Bd = torch.empty((K, N), dtype=torch.float64, device=dev) if rank == 0 else None
+            if not op.native:
+                return None                       # host operands go through the library's own multi-GPU layer only
 
             def e2e_step():
-                Ad.copy_(Ah, non_blocking=True)
-                if rank == 0:
-                    Bd.copy_(Bh, non_blocking=True)
-                op(Ad, Bd, C)
-                Ch.copy_(C, non_blocking=True)
-                torch.cuda.synchronize()
+                op.host(Ah, Bh, Ch)               # synchronous: returns when this rank's rows of C are back in host memory
             h2d, d2h = (M * K * world + K * N) * 8, M * N * 8 * world
-            how = "per rank: H2D of its rows of A (rank 0: and of B), the sharded product, D2H of its rows of C"
+            how = ("ozb_mg_dgemm(on_host=1) on every rank: B goes to rank 0's GPU in pieces that are broadcast as they land, every "
+                   "rank's rows of A and C travel in blocks beside the computation")
         e2e_step()
         self.barrier()
         t0 = time.perf_counter()
@@ -601,8 +597,8 @@ class Bench:
             e2e_step()
         self.barrier()
         dt = self.max_over_ranks((time.perf_counter() - t0) / steps)
-        if world == 1 and not torch.equal(Ch.to(dev), C):
-            raise RuntimeError("host-staged result differs from the device-resident result")
+        if not torch.equal(Ch.to(dev), C):
+            raise RuntimeError(f"rank {rank}: the host-staged result differs from the device-resident result")
         return {"value": flops_step / dt / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": dt * 1e3, "steps": steps, "how": how}
 

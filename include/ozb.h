@@ -179,6 +179,11 @@ int ozb_mg_info(ozb_mg *g, int *layout, int *pieces);
 int ozb_dgemm_norm(int M, int N, int K, const double *A, long long lda, const double *B, long long ldb, double *C, long long ldc,
                    int moduli, void *stream);
 
+/* bench/oz_strassen.cu:78-97 (scales_norm) alone, as a stage: the 2-norm scales of the `nvec` rows (by_rows = 1: rows of
+ * `len` contiguous doubles, pitch ldx) or of the `nvec` columns (by_rows = 0: a row-major len x nvec matrix, pitch ldx) for
+ * `moduli` moduli, beta = floor((log2 P - 1.001) / 2) as bench/oz_strassen.cu:247 sets it. Asynchronous. */
+int ozb_scales_norm(const double *X, int nvec, int len, long long ldx, int by_rows, int moduli, int *s, void *stream);
+
 /* src/ozaki_dd.cuh:143-148 (oz::ddgemm_t) -- the double-double product with leading dimensions (elements), the
  * reference's mode (0: C = AB, 1: C -= AB, 2: C = -AB, used by its LU solvers to update blocks in place), a modulus
  * count in {24, 28, 32} and a stream; device pointers, no final synchronisation. */

@@ -743,6 +743,15 @@ OZB_API int ozb_dgemm_norm(int M, int N, int K, const double *A, long long lda, 
         return (int)e;
     });
 }
+OZB_API int ozb_scales_norm(const double *X, int nvec, int len, long long ldx, int by_rows, int moduli, int *s, void *stream) {
+    if (int e = check_args(nvec, 1, len)) return e;
+    if (moduli < 8 || moduli > 16 || !X || !s || ldx < (by_rows ? len : nvec)) return OZB_EARG;
+    double l2 = 0;
+    for (int l = 0; l < moduli; l++) l2 += log2((double)modulus(l));
+    int beta = (int)floor((l2 - 1.001) / 2);
+    if (beta > 62) beta = 62;
+    return (int)scales_norm_only(X, nvec, len, ldx, by_rows ? 1 : 0, beta, s, (cudaStream_t)stream);
+}
 OZB_API int ozb_scale_residues_rows(int moduli, const double *X, int rows, int len, long long ldx, int bits, int *s, int8_t *R,
                                     int ld, size_t plane, void *stream) {
     if (int e = check_args(rows, 1, len)) return e;

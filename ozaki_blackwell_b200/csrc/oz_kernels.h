@@ -13,6 +13,7 @@ cudaError_t scale_residues_cols(int nm, const double *X, int rows, int cols, lon
 cudaError_t cols_absmax_accumulate(const double *X, int rows, int cols, long long ldx, unsigned long long *colmax, cudaStream_t st);
 cudaError_t cols_residues_from_max(int nm, const double *X, int rows, int cols, long long ldx, int bits, const unsigned long long *colmax,
                                    int *s, int8_t *R, int ld, size_t plane, cudaStream_t st);
+cudaError_t scales_norm_only(const double *X, int nvec, int len, long long ldx, int by_rows, int beta, int *s, cudaStream_t st);
 cudaError_t norm_scale_residues_rows(int nm, const double *X, int rows, int len, long long ldx, int beta, int *s, int8_t *R, int ld,
                                      size_t plane, cudaStream_t st);
 cudaError_t norm_scale_residues_cols(int nm, const double *X, int rows, int cols, long long ldx, int beta, int *s, int8_t *R, int ld,

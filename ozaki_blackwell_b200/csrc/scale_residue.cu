@@ -329,6 +329,12 @@ static cudaError_t launch_rows_given_t(const double *X, int rows, int len, long 
     row_scale_residues<NM, RR, MAXT, true><<<rows, nt, 0, st>>>(X, len, ldx, 0, s, R, ld, plane);
     return cudaGetLastError();
 }
+// The 2-norm scales alone: of `nvec` rows of a row-major matrix (by_rows) or of its `nvec` columns
+cudaError_t scales_norm_only(const double *X, int nvec, int len, long long ldx, int by_rows, int beta, int *s, cudaStream_t st) {
+    if (by_rows) scales_norm_kernel<1><<<nvec, 256, 0, st>>>(X, nvec, len, ldx, 1, beta, s);
+    else scales_norm_kernel<4><<<(nvec + 3) / 4, 256, 0, st>>>(X, nvec, len, 1, ldx, beta, s);
+    return cudaGetLastError();
+}
 // The 2-norm mode of both operands: scales first (reference order of summation), then the residue passes with those scales
 cudaError_t norm_scale_residues_rows(int nm, const double *X, int rows, int len, long long ldx, int beta, int *s, int8_t *R, int ld,
                                      size_t plane, cudaStream_t st) {

@@ -54,6 +54,40 @@ def test_config4_family_sampled():
     assert _same(got, want)
 
 
+@pytest.mark.parametrize("name", ["normal_k256", "normal_k7168", "wide_k384", "tiny_k128"])
+def test_kernel_reproduces_the_reference_superaccumulator(name):
+    """The stored outputs of the reference's own exact_dot (llm/ultra.cu:336-369 of the reference; BF16-valued scales, which
+    both definitions share): the kernel must return the same bits."""
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden"))
+    import f8_cases
+    golden = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "exact_f8_reference.npz"))
+    X, W, S = f8_cases.inputs(name)
+    rc, Y, opn, nm = _run(X, W, S)
+    assert rc == 0
+    nan = np.isnan(Y)
+    assert opn == int(nan.sum())
+    want = golden[name].view(np.float32)
+    assert _same(Y[~nan], want[~nan])
+    if name != "wide_k384":                       # 60 binades inside one row exceed the window: some outputs may stay open there
+        assert opn == 0
+
+
+def test_config4_full_size_sampled():
+    """BASELINE's rectangular configuration at its stated size: 2048 x 7168 times 7168 x 18432 with one FP32 scale per
+    128 x 128 block. Nothing may be left open, and a few hundred sampled outputs must be the exactly rounded sums."""
+    M, N, K = 2048, 18432, 7168
+    X, W, S = x.synthetic(M, N, K, 4)
+    rc, Y, opn, nm = _run(X, W, S)
+    assert rc == 0 and opn == 0 and 8 <= nm <= 19
+    assert not np.isnan(Y).any()
+    rng = np.random.default_rng(1)
+    entries = [(int(i), int(j)) for i, j in zip(rng.integers(0, M, 300), rng.integers(0, N, 300))]
+    entries += [(0, 0), (M - 1, N - 1), (0, N - 1), (M - 1, 0)]
+    want = x.product(X, W, S, entries)
+    got = np.array([Y[i, j] for i, j in entries], dtype=np.float32)
+    assert _same(got, want), f"{(got.view(np.uint32) != want.view(np.uint32)).sum()} of {len(entries)} sampled outputs differ"
+
+
 def test_signs_zeros_subnormals_and_wide_scales():
     M, N, K = 12, 260, 384
     X, W, S = x.synthetic(M, N, K, 5)
