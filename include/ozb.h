@@ -242,6 +242,15 @@ int ozb_int8_peak(int iters, int pair, float *ms, double *tops);
  * waits, with a budget of budget_ms (1..2000), on a barrier that nothing completes. The expected return value is
  * OZB_ETIMEOUT: the wait gave up, raised the status word and the kernel returned normally; the context stays usable. */
 int ozb_selftest_wait_expiry(int budget_ms);
+/* No counterpart in the reference (its debugging aid is a poison fill of the workspaces, src/ozaki_hol.cuh:498). The
+ * checked-access debug build of this library (libozaki_blackwell_bounds.so, compiled with -DOZ_BOUNDS) tests every global
+ * load and store of the scale / residue / reconstruction kernels and of the GEMM epilogue against the exact bytes the
+ * launch is entitled to; an access outside is skipped and recorded. ozb_bounds_report synchronises the device, returns
+ * out[0] = violations since the last call, out[1] = address, out[2] = kernel id, out[3] = size of the first one, and clears
+ * the record. ozb_selftest_bounds makes one checked store just outside a registered window and expects it to be skipped;
+ * the following ozb_bounds_report then shows exactly one violation. Both return OZB_ENOTBUILT in the normal build. */
+int ozb_bounds_report(unsigned long long out[4]);
+int ozb_selftest_bounds(void);
 /* Status of the stage calls above (they share one status word per device) and of the cached plans behind ozb_dgemm_ex,
  * ozb_dgemm_norm and ozb_ddgemm_ex on the current device: 0 or OZB_ETIMEOUT. Synchronises the device. */
 int ozb_status(void);

@@ -117,6 +117,13 @@ static int plan_make(int M, int N, int K, int nm, int maxbits, ozb_plan **out) {
     if (!e) e = cudaMalloc(&p->status, 256);
     if (!e) e = cudaMemset(p->status, 0, 256);
     if (!e) e = cudaEventCreateWithFlags(&p->evDone, cudaEventDisableTiming);
+#ifdef OZ_BOUNDS
+    // debug build: the workspaces start out poisoned (as the reference does, src/ozaki_hol.cuh:498), so a byte that is read
+    // without having been written shows up in the result
+    if (!e) e = cudaMemset(p->Ar, 0x7B, nm * p->planeA);
+    if (!e) e = cudaMemset(p->Br, 0x7B, nm * p->planeB);
+    if (!e) e = cudaMemset(p->Cr, 0x7B, nm * p->planeC);
+#endif
     // panels: one by default; OZ_PANELS = 2..8 splits the columns and overlaps the stages of different panels
     p->panel_width = round_up(N, 256); p->panels = 1;
     {
@@ -819,6 +826,45 @@ OZB_API int ozb_selftest_wait_expiry(int budget_ms) {
     if (int e = (int)wait_expiry_selftest((unsigned)budget_ms, st, 0)) return e == (int)cudaErrorInvalidValue ? OZB_EARG : e;
     if (int e = (int)cudaDeviceSynchronize()) return e;
     return read_status(st);
+}
+OZB_API int ozb_bounds_report(unsigned long long out[4]) {
+#ifdef OZ_BOUNDS
+    if (!out) return OZB_EARG;
+    if (int e = (int)cudaDeviceSynchronize()) return e;
+    std::lock_guard<std::mutex> g(mu);
+    unsigned long long v[3][4] = {};
+    cudaError_t e = scale_residue_violations(v[0]);
+    if (!e) e = crt_violations(v[1]);
+    if (!e) e = gemm_violations(v[2]);
+    if (e) return (int)e;
+    out[0] = out[1] = out[2] = out[3] = 0;
+    for (auto &w : v) {
+        if (w[0] && !out[0]) { out[1] = w[1]; out[2] = w[2]; out[3] = w[3]; }
+        out[0] += w[0];
+    }
+    return 0;
+#else
+    (void)out;
+    return OZB_ENOTBUILT;
+#endif
+}
+OZB_API int ozb_selftest_bounds(void) {
+#ifdef OZ_BOUNDS
+    if (int e = check_args(1, 1, 1)) return e;
+    int *buf = nullptr;
+    if (cudaError_t e = cudaMalloc(&buf, 8 * sizeof(int))) return (int)e;   // eight ints allocated, four registered
+    cudaError_t e = cudaMemset(buf, 0xFF, 8 * sizeof(int));
+    if (!e) e = bounds_selftest(buf, 0);
+    if (!e) e = cudaDeviceSynchronize();
+    int h[8] = {};
+    if (!e) e = cudaMemcpy(h, buf, sizeof h, cudaMemcpyDeviceToHost);
+    cudaFree(buf);
+    if (e) return (int)e;
+    for (int i = 0; i < 4; i++) if (h[i] != i) return OZB_EARG;            // the stores inside the window happened
+    return h[4] == -1 ? 0 : OZB_EARG;                                     // the one outside did not
+#else
+    return OZB_ENOTBUILT;
+#endif
 }
 OZB_API int ozb_status(void) {
     if (int e = (int)cudaDeviceSynchronize()) return e;

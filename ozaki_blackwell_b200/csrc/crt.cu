@@ -13,6 +13,7 @@
 // Input is either the GEMM epilogue's int8 planes of already balanced residues (16 bytes per element at 16 moduli
 // instead of 64) or, for the reference's layout, int32 planes of raw products.
 #include "oz_common.cuh"
+#include "oz_bounds.cuh"
 
 namespace ozk {
 
@@ -111,7 +112,7 @@ __global__ void __launch_bounds__(256) crt_kernel(const In *__restrict__ Cp, siz
             uint32_t w[4], t[4];
 #pragma unroll
             for (int p = 0; p < 4; p++)
-                w[p] = 4 * g + p < NM ? __ldg(reinterpret_cast<const uint32_t *>(base + (size_t)(4 * g + p) * plane)) : 0u;
+                w[p] = 4 * g + p < NM ? oz_load(reinterpret_cast<const uint32_t *>(base + (size_t)(4 * g + p) * plane)) : 0u;
             transpose4x4(w, t);
 #pragma unroll
             for (int e = 0; e < 4; e++) E[e][g] = t[e];
@@ -125,31 +126,34 @@ __global__ void __launch_bounds__(256) crt_kernel(const In *__restrict__ Cp, siz
             if (j0 + e < N) {
                 static_for<0, NM>([&](auto L) {
                     constexpr int l = decltype(L)::value;
-                    const int r = balanced_of_i32<l>(base[(size_t)l * plane + e]);
+                    const int r = balanced_of_i32<l>(oz_load(base + (size_t)l * plane + e));
                     E[e][l / 4] |= (uint32_t)(r & 255) << (8 * (l % 4));
                 });
             }
         }
     }
     garner_digits<NM, 4>(E);
-    const int si = sa[i];
+    const int si = oz_load(sa + i);
     double out[4];
 #pragma unroll
-    for (int e = 0; e < 4; e++) out[e] = j0 + e < N ? unscale(horner<NM>(E[e]), -(si + sb[j0 + e])) : 0.0;
+    for (int e = 0; e < 4; e++) out[e] = j0 + e < N ? unscale(horner<NM>(E[e]), -(si + oz_load(sb + j0 + e))) : 0.0;
     double *dst = C + (size_t)i * ldc + j0;
     if (j0 + 3 < N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-        reinterpret_cast<double2 *>(dst)[0] = make_double2(out[0], out[1]);
-        reinterpret_cast<double2 *>(dst)[1] = make_double2(out[2], out[3]);
+        oz_store(reinterpret_cast<double2 *>(dst), make_double2(out[0], out[1]));
+        oz_store(reinterpret_cast<double2 *>(dst) + 1, make_double2(out[2], out[3]));
     } else {
 #pragma unroll
         for (int e = 0; e < 4; e++)
-            if (j0 + e < N) dst[e] = out[e];
+            if (j0 + e < N) oz_store(dst + e, out[e]);
     }
 }
 
 template <int NM, class In>
 static cudaError_t launch_crt_t(const In *Cp, size_t plane, int M, int N, long long ldr, const int *sa, const int *sb, double *C,
                                 long long ldc, cudaStream_t st) {
+    // the int8 planes are read a 4-byte word at a time (rows readable up to the next multiple of 4 columns)
+    OZ_WINDOWS(st, OZK_CRT, window3d(Cp, NM, plane * sizeof(In), M, (size_t)ldr * sizeof(In), sizeof(In) == 1 ? (size_t)(N + 3) / 4 * 4 : (size_t)N * 4),
+               window1d(sa, (size_t)M * 4), window1d(sb, (size_t)N * 4), window2d(C, M, (size_t)ldc * 8, (size_t)N * 8));
     crt_kernel<NM, In><<<dim3(M, (N + 1023) / 1024), 256, 0, st>>>(Cp, plane, M, N, ldr, sa, sb, C, ldc);
     return cudaGetLastError();
 }
@@ -174,5 +178,8 @@ cudaError_t crt_from_i32(int nm, const int32_t *Cl, size_t plane, int M, int N, 
                          double *C, long long ldc, cudaStream_t st) {
     OZ_DISPATCH_NM(nm, (launch_crt_t<NM, int32_t>(Cl, plane, M, N, ldr, sa, sb, C, ldc, st)));
 }
+
+// violations the checked accesses of this file recorded since the last call (debug build; zeros otherwise)
+cudaError_t crt_violations(unsigned long long out[4]) { return oz_read_violations(out); }
 
 }  // namespace ozk

@@ -24,6 +24,7 @@
 #include <cstdlib>
 #include <mutex>
 #include "oz_common.cuh"
+#include "oz_bounds.cuh"
 
 namespace ozk {
 
@@ -156,8 +157,8 @@ __device__ __forceinline__ void store_piece(const Params &p, const ModConsts &mc
         int8_t *dst = reinterpret_cast<int8_t *>(p.C) + (size_t)z * p.plane_c + (size_t)row * p.ldc + col;
         uint32_t prev[8] = {};
         if (p.accumulate) {   // residues of the K chunks before this one: residues add, |sum| stays far below 2^31
-            if (col + 16 <= p.wcols) { const uint4 q = *reinterpret_cast<const uint4 *>(dst); prev[0] = q.x; prev[1] = q.y; prev[2] = q.z; prev[3] = q.w; }
-            if (col + 32 <= p.wcols) { const uint4 q = *reinterpret_cast<const uint4 *>(dst + 16); prev[4] = q.x; prev[5] = q.y; prev[6] = q.z; prev[7] = q.w; }
+            if (col + 16 <= p.wcols) { const uint4 q = oz_load(reinterpret_cast<const uint4 *>(dst)); prev[0] = q.x; prev[1] = q.y; prev[2] = q.z; prev[3] = q.w; }
+            if (col + 32 <= p.wcols) { const uint4 q = oz_load(reinterpret_cast<const uint4 *>(dst + 16)); prev[4] = q.x; prev[5] = q.y; prev[6] = q.z; prev[7] = q.w; }
         }
         uint32_t o[8];
 #pragma unroll
@@ -172,18 +173,18 @@ __device__ __forceinline__ void store_piece(const Params &p, const ModConsts &mc
             }
             o[g] = pack_low_bytes(x[0], x[1], x[2], x[3]);
         }
-        if (col + 16 <= p.wcols) *reinterpret_cast<uint4 *>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
-        if (col + 32 <= p.wcols) *reinterpret_cast<uint4 *>(dst + 16) = make_uint4(o[4], o[5], o[6], o[7]);
+        if (col + 16 <= p.wcols) oz_store(reinterpret_cast<uint4 *>(dst), make_uint4(o[0], o[1], o[2], o[3]));
+        if (col + 32 <= p.wcols) oz_store(reinterpret_cast<uint4 *>(dst + 16), make_uint4(o[4], o[5], o[6], o[7]));
     } else {
         int32_t *dst = reinterpret_cast<int32_t *>(p.C) + (size_t)z * p.plane_c + (size_t)row * p.ldc + col;
         if (col + 32 <= p.N && ((p.ldc | p.plane_c) & 3) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0) {
 #pragma unroll
             for (int g = 0; g < 8; g++)
-                reinterpret_cast<uint4 *>(dst)[g] = make_uint4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+                oz_store(reinterpret_cast<uint4 *>(dst) + g, make_uint4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]));
         } else {
 #pragma unroll
             for (int e = 0; e < 32; e++)
-                if (col + e < p.N) dst[e] = (int32_t)v[e];
+                if (col + e < p.N) oz_store(dst + e, (int32_t)v[e]);
         }
     }
 }
@@ -771,6 +772,8 @@ cudaError_t gemm_i8_planes(const int8_t *A, const int8_t *Bt, void *C, int M, in
     }
     const long long total = (long long)p.tiles_m * p.tiles_n * Z;
     if (total > 0x7fffffffLL) return cudaErrorInvalidValue;
+    // the epilogue's entitlement: rows [0, M) of every plane, whole 16-byte pieces up to wcols (fused) or N int32 (plain)
+    OZ_WINDOWS(st, OZK_GEMM_EPILOGUE, fused ? window3d(C, Z, pc, M, (size_t)ldc, (size_t)p.wcols) : window3d(C, Z, pc * 4, M, (size_t)ldc * 4, (size_t)N * 4));
     if (pair) {
         // A persistent grid must be fully resident: ask how many 2-CTA clusters of this kernel the device can hold at once
         static int max_pairs[64][2] = {};   // per device
@@ -851,5 +854,21 @@ cudaError_t wait_expiry_selftest(unsigned budget_ms, int *status, cudaStream_t s
     g8::wait_expiry_selftest<<<1, 32, 0, st>>>((unsigned long long)budget_ms * 1000000ull, status);
     return cudaGetLastError();
 }
+
+// violations the checked accesses of this file recorded since the last call (debug build; zeros otherwise)
+cudaError_t gemm_violations(unsigned long long out[4]) { return oz_read_violations(out); }
+
+#ifdef OZ_BOUNDS
+// Self-test of the checker itself: a checked store one element past a registered window of four ints. The store is not
+// performed and the violation is recorded; nothing touches memory it should not.
+__global__ void bounds_selftest_kernel(int *buf) { oz_store(buf + threadIdx.x, (int)threadIdx.x); }
+cudaError_t bounds_selftest(int *buf5, cudaStream_t st) {
+    OZ_WINDOWS(st, OZK_SELFTEST, window1d(buf5, 4 * sizeof(int)));
+    bounds_selftest_kernel<<<1, 5, 0, st>>>(buf5);   // thread 4 is the one outside
+    return cudaGetLastError();
+}
+#else
+cudaError_t bounds_selftest(int *, cudaStream_t) { return cudaErrorNotSupported; }
+#endif
 
 }  // namespace ozk

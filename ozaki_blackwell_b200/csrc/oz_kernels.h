@@ -28,6 +28,12 @@ cudaError_t crt_from_i8(int nm, const int8_t *Cr, size_t plane, int M, int N, lo
 cudaError_t crt_from_i32(int nm, const int32_t *Cl, size_t plane, int M, int N, long long ldr, const int *sa, const int *sb,
                          double *C, long long ldc, cudaStream_t st);
 
+// checked-access debug build (oz_bounds.cuh): per-file violation words and the checker's self-test
+cudaError_t scale_residue_violations(unsigned long long out[4]);
+cudaError_t crt_violations(unsigned long long out[4]);
+cudaError_t gemm_violations(unsigned long long out[4]);
+cudaError_t bounds_selftest(int *buf5, cudaStream_t st);
+
 // double-double path (dd.cu); nm in {24, 28, 32}
 cudaError_t dd_scale_residues_rows(int nm, const double *Xh, const double *Xl, int rows, int len, long long ldx, int bits, int *s,
                                    int8_t *R, int ld, size_t plane, cudaStream_t st);

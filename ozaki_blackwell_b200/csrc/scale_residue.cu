@@ -13,6 +13,7 @@
 // and one multiply-high reduction of a 19-bit sum, instead of a 64-bit division by a constant.
 #include <mutex>
 #include "oz_common.cuh"
+#include "oz_bounds.cuh"
 
 namespace ozk {
 
@@ -67,11 +68,11 @@ __global__ void __launch_bounds__(MAXT, OZ_ROW_MINB) row_scale_residues(const do
     auto load4 = [&](int c, double (&d)[4]) {
         const int k = c << 2;
         if (vec && k + 3 < len) {
-            const double2 a = *reinterpret_cast<const double2 *>(row + k), b = *reinterpret_cast<const double2 *>(row + k + 2);
+            const double2 a = oz_load(reinterpret_cast<const double2 *>(row + k)), b = oz_load(reinterpret_cast<const double2 *>(row + k + 2));
             d[0] = a.x; d[1] = a.y; d[2] = b.x; d[3] = b.y;
         } else {
 #pragma unroll
-            for (int e = 0; e < 4; e++) d[e] = k + e < len ? row[k + e] : 0.0;
+            for (int e = 0; e < 4; e++) d[e] = k + e < len ? oz_load(row + k + e) : 0.0;
         }
     };
     if (cached) {
@@ -93,7 +94,7 @@ __global__ void __launch_bounds__(MAXT, OZ_ROW_MINB) row_scale_residues(const do
     }
     int s;
     if constexpr (GIVEN) {
-        s = s_out[r];
+        s = oz_load(s_out + r);
     } else {
         // block max: shuffles inside the warp, shared memory across warps
         __shared__ double wmax[32];
@@ -104,7 +105,7 @@ __global__ void __launch_bounds__(MAXT, OZ_ROW_MINB) row_scale_residues(const do
         mx = wmax[0];
         for (int w = 1; w < (nt >> 5); w++) mx = fmax(mx, wmax[w]);
         s = scale_from_max(mx, bits);
-        if (tid == 0) s_out[r] = s;
+        if (tid == 0) oz_store(s_out + r, s);
     }
 
     const bool fast = s >= -1022 && s <= 1023;
@@ -115,7 +116,7 @@ __global__ void __launch_bounds__(MAXT, OZ_ROW_MINB) row_scale_residues(const do
 #pragma unroll
         for (int e = 0; e < 4; e++) v[e] = scaled_int(d[e], s, p2, fast);
         residues_of_4<NM>(v, [&](auto L, uint32_t word) {
-            *reinterpret_cast<uint32_t *>(out + decltype(L)::value * plane + ((size_t)c << 2)) = word;
+            oz_store(reinterpret_cast<uint32_t *>(out + decltype(L)::value * plane + ((size_t)c << 2)), word);
         });
     };
     if (cached) {
@@ -149,18 +150,18 @@ __global__ void __launch_bounds__(256) col_absmax(const double *__restrict__ X, 
     if (pair) {
 #pragma unroll 8
         for (int k = k0; k < k1; k++) {
-            const double2 d = *reinterpret_cast<const double2 *>(X + (size_t)k * ldx + j);
+            const double2 d = oz_load(reinterpret_cast<const double2 *>(X + (size_t)k * ldx + j));
             m0 = fmax(m0, fabs(d.x));
             m1 = fmax(m1, fabs(d.y));
         }
     } else {
         for (int k = k0; k < k1; k++) {
-            m0 = fmax(m0, fabs(X[(size_t)k * ldx + j]));
-            if (j + 1 < cols) m1 = fmax(m1, fabs(X[(size_t)k * ldx + j + 1]));
+            m0 = fmax(m0, fabs(oz_load(X + (size_t)k * ldx + j)));
+            if (j + 1 < cols) m1 = fmax(m1, fabs(oz_load(X + (size_t)k * ldx + j + 1)));
         }
     }
-    if (m0 != 0) atomicMax(colmax + j, (unsigned long long)__double_as_longlong(m0));
-    if (j + 1 < cols && m1 != 0) atomicMax(colmax + j + 1, (unsigned long long)__double_as_longlong(m1));
+    if (m0 != 0) oz_atomic_max(colmax + j, (unsigned long long)__double_as_longlong(m0));
+    if (j + 1 < cols && m1 != 0) oz_atomic_max(colmax + j + 1, (unsigned long long)__double_as_longlong(m1));
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -187,13 +188,13 @@ __global__ void __launch_bounds__(256, OZ_COL_MINB) col_residues_t(const double 
         const int j = j0 + lane, k0 = kb + warp * 16;
         if (j < cols && k0 < rows) {
             // colmax == nullptr: the scales are already in s_out (2-norm mode)
-            const int s = colmax ? scale_from_max(__longlong_as_double((long long)colmax[j]), bits) : s_out[j];
-            if (colmax && blockIdx.y == 0 && warp == 0) s_out[j] = s;
+            const int s = colmax ? scale_from_max(__longlong_as_double((long long)oz_load(colmax + j)), bits) : oz_load(s_out + j);
+            if (colmax && blockIdx.y == 0 && warp == 0) oz_store(s_out + j, s);
             const bool fast = s >= -1022 && s <= 1023;
             const double p2 = pow2_normal(fast ? s : 0);
             double d[16];
 #pragma unroll
-            for (int e = 0; e < 16; e++) d[e] = k0 + e < rows ? X[(size_t)(k0 + e) * ldx + j] : 0.0;
+            for (int e = 0; e < 16; e++) d[e] = k0 + e < rows ? oz_load(X + (size_t)(k0 + e) * ldx + j) : 0.0;
             uint32_t w[NM][4];
 #pragma unroll
             for (int q = 0; q < 4; q++) {
@@ -216,7 +217,7 @@ __global__ void __launch_bounds__(256, OZ_COL_MINB) col_residues_t(const double 
         const int j = threadIdx.x >> 3, l = i;
         if (j0 + j < cols) {
             const uint4 v = *reinterpret_cast<const uint4 *>(tile + (l * CT_COLS + j) * CT_PITCH + c * 16);
-            *reinterpret_cast<uint4 *>(Rp + (size_t)l * plane + (size_t)(j0 + j) * ld + kpos) = v;
+            oz_store(reinterpret_cast<uint4 *>(Rp + (size_t)l * plane + (size_t)(j0 + j) * ld + kpos), v);
         }
     }
 }
@@ -241,7 +242,7 @@ __global__ void __launch_bounds__(256) scales_norm_kernel(const double *__restri
     for (int k = tid; k < len; k += 256)
 #pragma unroll
         for (int q = 0; q < VECS; q++)
-            if (v0 + q < nvec) acc[q] = fmax(acc[q], fabs(X[(size_t)(v0 + q) * sVec + (size_t)k * sElem]));
+            if (v0 + q < nvec) acc[q] = fmax(acc[q], fabs(oz_load(X + (size_t)(v0 + q) * sVec + (size_t)k * sElem)));
 #pragma unroll
     for (int q = 0; q < VECS; q++) {
         for (int o = 16; o; o >>= 1) acc[q] = fmax(acc[q], __shfl_xor_sync(~0u, acc[q], o));
@@ -261,7 +262,7 @@ __global__ void __launch_bounds__(256) scales_norm_kernel(const double *__restri
     for (int k = tid; k < len; k += 256)
 #pragma unroll
         for (int q = 0; q < VECS; q++)
-            if (v0 + q < nvec) { const double v = ldexp(X[(size_t)(v0 + q) * sVec + (size_t)k * sElem], -e[q]); acc[q] = fma(v, v, acc[q]); }
+            if (v0 + q < nvec) { const double v = ldexp(oz_load(X + (size_t)(v0 + q) * sVec + (size_t)k * sElem), -e[q]); acc[q] = fma(v, v, acc[q]); }
     __syncthreads();   // w is reused
 #pragma unroll
     for (int q = 0; q < VECS; q++) {
@@ -272,7 +273,7 @@ __global__ void __launch_bounds__(256) scales_norm_kernel(const double *__restri
     if (tid < VECS && v0 + tid < nvec) {
         double t = w[tid][0];
         for (int i = 1; i < 8; i++) t = t + w[tid][i];
-        s[v0 + tid] = zero[tid] ? 0 : beta - 1 - (se[tid] + ilogb(sqrt(t) * (1 + 0x1p-30)));
+        oz_store(s + v0 + tid, zero[tid] ? 0 : beta - 1 - (se[tid] + ilogb(sqrt(t) * (1 + 0x1p-30))));
     }
 }
 
@@ -290,22 +291,11 @@ static cudaError_t launch_rows_t(const double *X, int rows, int len, long long l
     nt = (nt + 31) / 32 * 32;
     if (nt < 32) nt = 32;
     if (nt > MAXT) nt = MAXT;
+    OZ_WINDOWS(st, OZK_ROW_RESIDUES, window2d(X, rows, (size_t)ldx * 8, (size_t)len * 8), window1d(s, (size_t)rows * 4),
+               window3d(R, NM, plane, rows, ld, (size_t)(len + 3) / 4 * 4));
     row_scale_residues<NM, RR, MAXT><<<rows, nt, 0, st>>>(X, len, ldx, bits, s, R, ld, plane);
     return cudaGetLastError();
 }
-template <int NM>
-static cudaError_t launch_cols_t(const double *X, int rows, int cols, long long ldx, int bits, unsigned long long *colmax,
-                                 int *s, int8_t *R, int ld, size_t plane, cudaStream_t st) {
-    cudaError_t e = cudaMemsetAsync(colmax, 0, (size_t)cols * 8, st);
-    if (e) return e;
-    col_absmax<<<dim3((cols + 511) / 512, (rows + CM_ROWS - 1) / CM_ROWS), 256, 0, st>>>(X, rows, cols, ldx, colmax);
-    static PerDevice pd;
-    if (cudaError_t a = pd.once([] { return cudaFuncSetAttribute(col_residues_t<NM>, cudaFuncAttributeMaxDynamicSharedMemorySize, col_tile_smem<NM>()); })) return a;
-    col_residues_t<NM><<<dim3((cols + CT_COLS - 1) / CT_COLS, (rows + CT_K - 1) / CT_K), 256, col_tile_smem<NM>(), st>>>(
-        X, rows, cols, ldx, colmax, bits, s, R, ld, plane);
-    return cudaGetLastError();
-}
-
 #define OZ_DISPATCH_NM(nm, CALL)                                                                                  \
     switch (nm) {                                                                                                 \
     case 8: { constexpr int NM = 8; return CALL; }    case 9: { constexpr int NM = 9; return CALL; }              \
@@ -326,11 +316,15 @@ static cudaError_t launch_rows_given_t(const double *X, int rows, int len, long 
     nt = (nt + 31) / 32 * 32;
     if (nt < 32) nt = 32;
     if (nt > MAXT) nt = MAXT;
+    OZ_WINDOWS(st, OZK_ROW_RESIDUES, window2d(X, rows, (size_t)ldx * 8, (size_t)len * 8), window1d(s, (size_t)rows * 4),
+               window3d(R, NM, plane, rows, ld, (size_t)(len + 3) / 4 * 4));
     row_scale_residues<NM, RR, MAXT, true><<<rows, nt, 0, st>>>(X, len, ldx, 0, s, R, ld, plane);
     return cudaGetLastError();
 }
 // The 2-norm scales alone: of `nvec` rows of a row-major matrix (by_rows) or of its `nvec` columns
 cudaError_t scales_norm_only(const double *X, int nvec, int len, long long ldx, int by_rows, int beta, int *s, cudaStream_t st) {
+    if (by_rows) OZ_WINDOWS(st, OZK_SCALES_NORM, window2d(X, nvec, (size_t)ldx * 8, (size_t)len * 8), window1d(s, (size_t)nvec * 4));
+    else OZ_WINDOWS(st, OZK_SCALES_NORM, window2d(X, len, (size_t)ldx * 8, (size_t)nvec * 8), window1d(s, (size_t)nvec * 4));
     if (by_rows) scales_norm_kernel<1><<<nvec, 256, 0, st>>>(X, nvec, len, ldx, 1, beta, s);
     else scales_norm_kernel<4><<<(nvec + 3) / 4, 256, 0, st>>>(X, nvec, len, 1, ldx, beta, s);
     return cudaGetLastError();
@@ -338,14 +332,12 @@ cudaError_t scales_norm_only(const double *X, int nvec, int len, long long ldx, 
 // The 2-norm mode of both operands: scales first (reference order of summation), then the residue passes with those scales
 cudaError_t norm_scale_residues_rows(int nm, const double *X, int rows, int len, long long ldx, int beta, int *s, int8_t *R, int ld,
                                      size_t plane, cudaStream_t st) {
-    scales_norm_kernel<1><<<rows, 256, 0, st>>>(X, rows, len, ldx, 1, beta, s);
-    if (cudaError_t e = cudaGetLastError()) return e;
+    if (cudaError_t e = scales_norm_only(X, rows, len, ldx, 1, beta, s, st)) return e;
     OZ_DISPATCH_NM(nm, (launch_rows_given_t<NM>(X, rows, len, ldx, s, R, ld, plane, st)));
 }
 cudaError_t norm_scale_residues_cols(int nm, const double *X, int rows, int cols, long long ldx, int beta, int *s, int8_t *R, int ld,
                                      size_t plane, cudaStream_t st) {
-    scales_norm_kernel<4><<<(cols + 3) / 4, 256, 0, st>>>(X, cols, rows, 1, ldx, beta, s);
-    if (cudaError_t e = cudaGetLastError()) return e;
+    if (cudaError_t e = scales_norm_only(X, cols, rows, ldx, 0, beta, s, st)) return e;
     return cols_residues_from_max(nm, X, rows, cols, ldx, 0, nullptr, s, R, ld, plane, st);
 }
 // A-like operand: `rows` rows of `len` contiguous doubles, row pitch ldx; writes s[rows] and R[nm][rows][ld]
@@ -357,6 +349,7 @@ cudaError_t scale_residues_rows(int nm, const double *X, int rows, int len, long
 // of rows [0, rows) of X accumulate into colmax (which the caller cleared once), the residue pass runs when all chunks
 // have been seen.
 cudaError_t cols_absmax_accumulate(const double *X, int rows, int cols, long long ldx, unsigned long long *colmax, cudaStream_t st) {
+    OZ_WINDOWS(st, OZK_COL_ABSMAX, window2d(X, rows, (size_t)ldx * 8, (size_t)cols * 8), window1d(colmax, (size_t)cols * 8));
     col_absmax<<<dim3((cols + 511) / 512, (rows + CM_ROWS - 1) / CM_ROWS), 256, 0, st>>>(X, rows, cols, ldx, colmax);
     return cudaGetLastError();
 }
@@ -365,6 +358,8 @@ static cudaError_t launch_cols_residues_t(const double *X, int rows, int cols, l
                                           int *s, int8_t *R, int ld, size_t plane, cudaStream_t st) {
     static PerDevice pd;
     if (cudaError_t a = pd.once([] { return cudaFuncSetAttribute(col_residues_t<NM>, cudaFuncAttributeMaxDynamicSharedMemorySize, col_tile_smem<NM>()); })) return a;
+    OZ_WINDOWS(st, OZK_COL_RESIDUES, window2d(X, rows, (size_t)ldx * 8, (size_t)cols * 8), window1d(colmax, colmax ? (size_t)cols * 8 : 0),
+               window1d(s, (size_t)cols * 4), window3d(R, NM, plane, cols, ld, (size_t)(rows + 15) / 16 * 16));
     col_residues_t<NM><<<dim3((cols + CT_COLS - 1) / CT_COLS, (rows + CT_K - 1) / CT_K), 256, col_tile_smem<NM>(), st>>>(
         X, rows, cols, ldx, colmax, bits, s, R, ld, plane);
     return cudaGetLastError();
@@ -376,7 +371,10 @@ cudaError_t cols_residues_from_max(int nm, const double *X, int rows, int cols, 
 // B-like operand: row-major `rows` x `cols` (rows = K), scaled per column; writes s[cols] and Rt[nm][cols][ld]
 cudaError_t scale_residues_cols(int nm, const double *X, int rows, int cols, long long ldx, int bits, unsigned long long *colmax,
                                 int *s, int8_t *R, int ld, size_t plane, cudaStream_t st) {
-    OZ_DISPATCH_NM(nm, (launch_cols_t<NM>(X, rows, cols, ldx, bits, colmax, s, R, ld, plane, st)));
+    cudaError_t e = cudaMemsetAsync(colmax, 0, (size_t)cols * 8, st);
+    if (!e) e = cols_absmax_accumulate(X, rows, cols, ldx, colmax, st);
+    if (e) return e;
+    return cols_residues_from_max(nm, X, rows, cols, ldx, bits, colmax, s, R, ld, plane, st);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -412,6 +410,9 @@ static unsigned long long *static_scratch_for_current_device(cudaError_t *err) {
     *err = cudaSuccess;
     return ptrs[dev];
 }
+
+// violations the checked accesses of this file recorded since the last call (debug build; zeros otherwise)
+cudaError_t scale_residue_violations(unsigned long long out[4]) { return oz_read_violations(out); }
 
 }  // namespace ozk
 

@@ -28,7 +28,7 @@ def test_checker_reproduces_the_reference_superaccumulator(name):
 
 def test_stored_cases_are_not_trivial():
     Y = GOLDEN["tiny_k128"].view(np.float32)
-    assert np.all(np.abs(Y) < 1.2e-38) and np.any(Y != 0)            # subnormal outputs: the rounding position is clamped
+    assert np.any((np.abs(Y) < 1.17e-38) & (Y != 0)) and np.abs(Y).max() < 1e-37   # subnormal outputs: the rounding position is clamped
     Y = GOLDEN["wide_k384"].view(np.float32)
     assert np.all(Y[1] == 0) and np.abs(Y).max() > 1e9               # a zero row, large magnitudes
 
