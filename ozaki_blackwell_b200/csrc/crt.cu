@@ -60,7 +60,14 @@ __device__ __forceinline__ void garner_digits(uint32_t (&X)[E][(NM + 3) / 4]) {
 // 2^52 (one permute), minus 2^52 + 128 (one add)
 template <int B>
 __device__ __forceinline__ double digit_to_double(uint32_t biased) {
+#ifdef OZ_OLD_DIGIT_CONV   // the earlier form, on the unbiased word: sign-extend the byte, flip the top bit, subtract 2^52 + 2^31
+    constexpr uint32_t sel = B == 0 ? 0x8880u : B == 1 ? 0x9991u : B == 2 ? 0xAAA2u : 0xBBB3u;
+    uint32_t v;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(v) : "r"(biased ^ 0x80808080u), "r"(0u), "r"(sel));
+    return __hiloint2double(0x43300000, (int)(v ^ 0x80000000u)) - 4503601774854144.0;
+#else
     return __hiloint2double(0x43300000, (int)__byte_perm(biased, 0u, 0x4440u + B)) - 4503599627370624.0;   // 2^52 + 128
+#endif
 }
 
 // the reference's Horner loop (src/ozaki2.cuh:93-95) on the packed digits of one element

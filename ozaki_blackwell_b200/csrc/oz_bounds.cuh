@@ -11,8 +11,8 @@
 // The GEMM's operand loads need no such check: they are TMA loads, bounded by the extents in their tensor maps.
 //
 // In a normal build oz_load / oz_store are plain accesses and OZ_WINDOWS expands to nothing.
-// The registered windows are one set per translation unit, written on the launch's stream just before the kernel: a
-// debug build must not run kernels of one file concurrently on several streams.
+// The registered windows are one set per translation unit, written on the launch's stream just before the kernel; the
+// debug build drains the device before every such write, so checked kernels never overlap (it tests addresses, not timing).
 #pragma once
 #include <cuda_runtime.h>
 
@@ -58,6 +58,9 @@ inline cudaError_t oz_set_windows(cudaStream_t st, int kernel, std::initializer_
     Windows h{};
     for (const Window &w : ws) if (h.n < MAX_WINDOWS) h.w[h.n++] = w;
     h.kernel = kernel;
+    // every checked kernel runs alone: the windows are one set per file, and kernels of one file may be queued on several
+    // streams (the multi-panel path), so the device is drained before the set is replaced
+    if (cudaError_t e = cudaDeviceSynchronize()) return e;
     return cudaMemcpyToSymbolAsync(g_windows, &h, sizeof h, 0, cudaMemcpyHostToDevice, st);   // pageable source: staged before the call returns
 }
 // count of violations in this translation unit since the last call (and the first one's details), then cleared

@@ -40,17 +40,24 @@ template <int L>
 __device__ __forceinline__ uint32_t mod_magic(uint32_t u) {
     return u - __umulhi(u, magic_of(L)) * (uint32_t)modulus(L);
 }
-// Balanced residue in one step less: `a` is a non-negative representative of the class that is already shifted down by
-// floor(m/2), i.e. a = S + (multiple of m) with S the signed sum. Then bal(S) = a - floor((a + floor(m/2)) / m) * m, and the
-// quotient is the high word of a * magic + floor(m/2) * magic: one wide multiply-add with a constant addend, one
-// multiply-add. Exact while a + floor(m/2) is below the bound checked by magic_ok(). Returns the residue as a 32-bit
-// two's-complement value (its low byte is the int8).
+// Balanced residue of a lifted sum: `a` is a non-negative representative of the class that is already shifted down by
+// floor(m/2), i.e. a = S + (multiple of m) with S the signed sum; bal(S) = (a + floor(m/2)) mod m - floor(m/2). One add, one
+// multiply-high, one multiply-add, one subtract. (Folding the add into the quotient with a 64-bit multiply-add and a
+// constant addend is exact too, but measured on B200 it executes MORE instructions: 86.0 M against 78.1 M warp instructions
+// for the residues of a 4096 x 4096 matrix -- the 64-bit constant costs more than the add it saves. -DOZ_FOLD_BALANCE keeps
+// that form for comparison.) Exact while a + floor(m/2) is below the bound checked by magic_ok(). Returns the residue as a
+// 32-bit two's-complement value (its low byte is the int8).
 template <int L>
 __device__ __forceinline__ uint32_t balanced_magic(uint32_t a) {
+#ifdef OZ_FOLD_BALANCE
     constexpr unsigned long long add = (unsigned long long)half_of(L) * magic_of(L);
     unsigned long long prod;
     asm("mad.wide.u32 %0, %1, %2, %3;" : "=l"(prod) : "r"(a), "r"(magic_of(L)), "l"(add));
     return a - (uint32_t)(prod >> 32) * (uint32_t)modulus(L);
+#else
+    const uint32_t u = a + (uint32_t)half_of(L);
+    return u - __umulhi(u, magic_of(L)) * (uint32_t)modulus(L) - (uint32_t)half_of(L);
+#endif
 }
 // 2^s as a double for -1022 <= s <= 1023
 __device__ __forceinline__ double pow2_normal(int s) { return __hiloint2double((s + 1023) << 20, 0); }

@@ -22,8 +22,11 @@ static int dp4a(uint32_t a, uint32_t b, int c, bool a_signed) {
 static uint32_t umulhi(uint32_t a, uint32_t b) { return (uint32_t)(((uint64_t)a * b) >> 32); }
 // oz_common.cuh: balanced_magic<L> -- the quotient of (a + floor(m/2)) / m from one wide multiply-add with a constant addend
 template <int L> static uint32_t balanced_magic(uint32_t a) {
-    const uint64_t prod = (uint64_t)a * magic_of(L) + (uint64_t)half_of(L) * magic_of(L);
-    return a - (uint32_t)(prod >> 32) * (uint32_t)modulus(L);
+    const uint32_t u = a + (uint32_t)half_of(L);
+    const uint32_t plain = u - umulhi(u, magic_of(L)) * (uint32_t)modulus(L) - (uint32_t)half_of(L);
+    const uint64_t prod = (uint64_t)a * magic_of(L) + (uint64_t)half_of(L) * magic_of(L);   // the folded form (-DOZ_FOLD_BALANCE)
+    const uint32_t folded = a - (uint32_t)(prod >> 32) * (uint32_t)modulus(L);
+    return plain == folded ? plain : 0x7fffffffu;   // both forms must agree; a disagreement shows up as a wrong residue
 }
 static int bal(long long x, int m) { return bal_c(x, m); }
 
