@@ -55,7 +55,7 @@ def peaks():
 
 def workload_config(n, nm, world):
     """The `config` object: the same in both arms for the same flags."""
-    return {"workload": f"FP64 GEMM n={n}, {nm} moduli (Ozaki-II), entries U[-1,1)*2^e, e in [-8,8], seeded; "
+    return {"workload": f"FP64 GEMM n={n}, {nm} moduli (Ozaki-II), entries U[-1,1)*2^e, e in [-{SPREAD},{SPREAD}], seeded; "
                         f"{world} row block(s) of {n} rows, B on rank 0",
             "moduli": nm, "n": n, "M_total": n * world, "parallelism": f"row-block x{world}",
             "l2": "operands (512 MiB each at n=8192) exceed L2; no flush needed"}
@@ -476,6 +476,8 @@ class Bench:
             same = bool(np.array_equal(Cs.view(np.uint64), C[:rows, :cols].cpu().numpy().view(np.uint64)))
             er = min(rows, 32)
             err = o.err_units(An[:er], Bn, Cs[:er])   # Dot2 reference, every entry of the first rows of the sample
+            if baselines and getattr(self, "cublas_rows", None) is not None:
+                baselines["cublas_dgemm"]["max_err_units_2^-53"] = o.err_units(An[:er], Bn, np.ascontiguousarray(self.cublas_rows[:er, :cols]))
             cpu = {"value": 2.0 * M * N * K / t_full / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
                    "sample": f"the {rows} x {cols} block of the product at the origin, all of K ({tb + ta + tg:.1f} s of CPU work); scaled to "
                              f"the whole product: B's pass by N/{cols}, A's by M/{rows}, GEMMs + reconstruction by both",
@@ -548,6 +550,7 @@ class Bench:
         out = {}
         t = med(lambda: torch.matmul(A, B, out=R))
         out["cublas_dgemm"] = {"ms": t, "tflops": fl / t, "what": "torch.matmul in float64 (cuBLAS DGEMM, native FP64)"}
+        self.cublas_rows = R[:32].cpu().numpy()          # its error is measured by the CPU leg on the same block as this library's
         ref_path = os.path.join(ROOT, "oracle", "_ref", "libozb_ref.so")
         if os.path.exists(ref_path):
             ref = ctypes.CDLL(ref_path)
@@ -628,6 +631,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--size", "--n", dest="n", type=int, default=8192, help="n of the n x n x n product (use --size under torchrun)")
     ap.add_argument("--moduli", type=int, default=16)
+    ap.add_argument("--spread", type=int, default=8, help="entries U[-1,1) * 2^e with e uniform in [-spread, spread] (0: plain U[-1,1))")
     ap.add_argument("--panels", type=int, default=None, help="pieces B is broadcast in (N > 1; default: by the size of B)")
     ap.add_argument("--layout", choices=("auto", "rows", "panels"), default="auto", help="broadcast B in row chunks or in column panels (N > 1)")
     ap.add_argument("--strong", action="store_true", help="make the headline run itself a strong split of the n x n x n product")
@@ -638,6 +642,8 @@ def main():
     ap.add_argument("--cpu-cols", type=int, default=4096, help="columns of the CPU baseline's block sample")
     ap.add_argument("--no-baselines", action="store_true", help="skip the reference-kernels and cuBLAS legs")
     args = ap.parse_args()
+    global SPREAD
+    SPREAD = args.spread
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 0)
     if args.impl == "reference":
         run_reference(args)

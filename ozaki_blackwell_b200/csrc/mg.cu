@@ -119,7 +119,11 @@ int mg_settle(ozb_mg *g, ncclResult_t r) {
 int mg_bcast(ozb_mg *g, void *buf, size_t bytes, int root) {
     if (g->world == 1) return 0;   // a single rank holds B already; the rest of the schedule is the same
     if (g->broken) return OZB_ECOMM;
-    return mg_settle(g, nccl().Broadcast(buf, buf, bytes, ncclChar, root, g->comm, g->sComm));
+    static const bool trace = getenv("OZ_MG_TRACE") != nullptr;   // host time of every enqueue, on stderr
+    const auto t0 = Clock::now();
+    const int rc = mg_settle(g, nccl().Broadcast(buf, buf, bytes, ncclChar, root, g->comm, g->sComm));
+    if (trace) fprintf(stderr, "ozb mg rank %d: broadcast of %zu bytes queued in %.3f ms (rc %d)\n", g->rank, bytes, ms_since(t0), rc);
+    return rc;
 }
 // waits for an event on the host, within the budget, watching the communicator: a product whose broadcast never completes
 // (a peer is gone) ends here with the communicator aborted instead of blocking in a synchronise call for ever
@@ -207,46 +211,43 @@ int mg_dgemm_dev(ozb_mg *g, int m, int N, int K, const double *A, long long lda,
     if (!e) e = cudaStreamWaitEvent(g->sComm, g->evDone, 0);
     if (e) return (int)e;
 
-    int rows = K, pieces = 1;
-    if (layout == LAYOUT_STREAM) {
-        static const size_t target = [] { const char *env = getenv("OZ_MG_PIECE_MB"); const int v = env && *env ? atoi(env) : 0; return (size_t)(v > 0 ? v : 512) << 20; }();
-        rows = piece_rows(K, N, target);
-        pieces = (K + rows - 1) / rows;
-        if (int c = mg_bcast(g, p->colmax, (size_t)N * 8, root)) return c;   // the column maxima, ahead of B
-    }
-    for (int i = 0; i < pieces; i++) {
-        const int k0 = i * rows, len = K - k0 < rows ? K - k0 : rows;
-        if (int c = mg_bcast(g, whole + (size_t)k0 * N, (size_t)len * N * 8, root)) return c;
-        if ((e = cudaEventRecord(g->evPiece[i], g->sComm))) return (int)e;
-    }
-    g->last_layout = layout; g->last_pieces = pieces;
-
-    // compute stream: the residues of A run beside the first transfer
+    // The host queues the residues of A first and then, piece by piece, the transfer and right behind it the work that
+    // consumes the piece (the compute stream waits for the arrival on the device). Queueing every transfer before any
+    // computation would leave the GPU without work while the host is still inside NCCL's enqueue calls, which take
+    // milliseconds each when several transfers are outstanding.
     e = scale_residues_rows(nm, A, m, K, lda, p->bits, p->sa, p->Ar, p->Kp, p->planeA, st);
+    if (e) return (int)e;
+    int pieces = 1;
     if (layout == LAYOUT_WHOLE) {
-        if (!e && !src) e = cudaStreamWaitEvent(st, g->evPiece[0], 0);
+        if (int c = mg_bcast(g, whole, (size_t)K * N * 8, root)) return c;
+        if ((e = cudaEventRecord(g->evPiece[0], g->sComm))) return (int)e;
+        if (!src) e = cudaStreamWaitEvent(st, g->evPiece[0], 0);
         if (!e) e = cols_absmax_accumulate(whole, K, N, N, p->colmax, st);
         if (!e) e = cols_residues_from_max(nm, whole, K, N, N, p->bits, p->colmax, p->sb, p->Br, p->Kp, p->planeB, st);
         if (!e) e = ozb_plan_gemm_range(p, N, 0, K, 0, st);
     } else {
+        static const size_t target = [] { const char *env = getenv("OZ_MG_PIECE_MB"); const int v = env && *env ? atoi(env) : 0; return (size_t)(v > 0 ? v : 1024) << 20; }();
         // K ranges of the GEMMs: a first short one (the product starts early), then about 8192 each, on piece boundaries
         static const int kchunk = [] { const char *env = getenv("OZ_KCHUNK"); const int v = env && *env ? atoi(env) : 0; return v >= 1024 ? v : 8192; }();
-        int done = 0, range_k0 = 0, ranges = 0;
-        if (!src) e = cudaStreamWaitEvent(st, g->evPiece[0], 0);   // the maxima were sent before the first piece on the same stream
+        const int rows = piece_rows(K, N, target);
+        pieces = (K + rows - 1) / rows;
+        if (int c = mg_bcast(g, p->colmax, (size_t)N * 8, root)) return c;   // the column maxima, ahead of B on the same stream
+        int range_k0 = 0, ranges = 0;
         for (int i = 0; i < pieces && !e; i++) {
-            const int k0 = i * rows, len = K - k0 < rows ? K - k0 : rows;
-            if (!src && i > 0) e = cudaStreamWaitEvent(st, g->evPiece[i], 0);
+            const int k0 = i * rows, len = K - k0 < rows ? K - k0 : rows, done = k0 + len;
+            if (int c = mg_bcast(g, whole + (size_t)k0 * N, (size_t)len * N * 8, root)) return c;
+            if ((e = cudaEventRecord(g->evPiece[i], g->sComm))) break;
+            if (!src) e = cudaStreamWaitEvent(st, g->evPiece[i], 0);
             if (!e) e = cols_residues_from_max(nm, whole + (size_t)k0 * N, len, N, N, p->bits, p->colmax, p->sb, p->Br + k0, p->Kp, p->planeB, st);
-            done = k0 + len;
             const int want = ranges == 0 ? kchunk / 2 : kchunk;
-            const bool last = i == pieces - 1;
             // close the range when it is long enough, unless what would remain is too short to be a range of its own
-            if (!e && (last || (done - range_k0 >= want && K - done >= kchunk / 4))) {
+            if (!e && (i == pieces - 1 || (done - range_k0 >= want && K - done >= kchunk / 4))) {
                 e = ozb_plan_gemm_range(p, N, range_k0, done - range_k0, ranges > 0, st);
                 range_k0 = done; ranges++;
             }
         }
     }
+    g->last_layout = layout; g->last_pieces = pieces;
     if (!e) e = crt_from_i8(nm, p->Cr, p->planeC, m, N, p->Np, p->sa, p->sb, C, ldc, st);
     // the holder's stream also waits for the sends: the caller may overwrite B (or the next call the staging copy) after this call
     if (!e && src) e = cudaStreamWaitEvent(st, g->evPiece[pieces - 1], 0);
@@ -394,8 +395,12 @@ OZB_API void ozb_mg_destroy(ozb_mg *g) {
     cudaGetDevice(&cur);
     if (cur != dev) cudaSetDevice(dev);
     if (g->comm && !g->broken) {
-        cudaStreamSynchronize(g->sComm);
-        nccl().CommDestroy(g->comm);
+        // Tear-down must not depend on the peers: ncclCommDestroy of a live communicator may wait for them (a rank that
+        // leaves on its own would block there), ncclCommAbort releases the local resources whatever the others do. The
+        // handle's own transfers have been waited for by then (every product ends with ozb_mg_wait or a synchronous call).
+        cudaEvent_t idle = g->evStart;
+        if (cudaEventRecord(idle, g->sComm) == cudaSuccess) drain(idle, g->timeout_ms);
+        nccl().CommAbort(g->comm);
     }
     if (g->plan) ozb_plan_free_internal(g->plan);
     cudaFree(g->stageB); cudaFree(g->dA); cudaFree(g->dC);
