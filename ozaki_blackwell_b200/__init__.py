@@ -133,10 +133,16 @@ def _call(entry, left, right, n_results, trailing, out):
     return results
 
 
-def matmul(a, b, moduli=16, out=None):
+def matmul(a, b, moduli=16, out=None, devices=1):
     """A @ B with FP64 accuracy. `moduli` (8..16) is the reference's accuracy/speed knob: 16 gives full FP64 accuracy for
-    entries spread over 2^+-16, fewer moduli are faster and coarser. `out`: an array to receive the result."""
-    return _call(_lib.ozb_dgemm, [a], [b], 1, [int(moduli)], None if out is None else [out])[0]
+    entries spread over 2^+-16, fewer moduli are faster and coarser. `out`: an array to receive the result.
+    `devices` > 1 (an addition; the reference is single-GPU) splits the rows of A and C over GPUs 0 .. devices-1 of this
+    machine, with B broadcast over NVLink; the result has the same bits."""
+    entry = _lib.ozb_dgemm
+    if int(devices) > 1:
+        def entry(*args):
+            return _lib.ozb_dgemm_mg(*args, int(devices))
+    return _call(entry, [a], [b], 1, [int(moduli)], None if out is None else [out])[0]
 
 
 def matmul_dd(a, b, out=None):

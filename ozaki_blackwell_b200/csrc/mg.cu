@@ -170,22 +170,28 @@ int mg_plan(ozb_mg *g, int m, int N, int K, int nm) {
     return 0;
 }
 
-// rows per piece of a K x N matrix sent in pieces of about `target` bytes: a multiple of 128 rows, at most MG_MAX_PIECES pieces
+// rows per piece of a K x N matrix sent in pieces of about `target` bytes: a multiple of 128 rows, fewer than MG_MAX_PIECES pieces
 int piece_rows(int K, int N, size_t target) {
     long long rows = (long long)(target / ((size_t)N * 8)) / 128 * 128;
     if (rows < 128) rows = 128;
-    while ((K + rows - 1) / rows > MG_MAX_PIECES) rows += 128;
+    while ((K + rows - 1) / rows > MG_MAX_PIECES - 1) rows += 128;   /* one more piece may be split off the front */
     return (int)rows;
 }
 
 enum { LAYOUT_WHOLE = 0, LAYOUT_STREAM = 1 };
-int choose_layout(int K, int N) {
+// One transfer, or pieces consumed as they land? Streaming costs a pass over B on the holder before anything can be sent,
+// one more GEMM launch and NCCL's kernels beside the GEMMs; it pays when the transfer is long against this rank's share
+// of the product. Measured on B200s with n = 32768: two ranks (16384 rows each, 8 GiB of B) 216.1 ms in one transfer
+// against 222.9 - 225.1 ms in 4 - 8 pieces; with 4096 rows per rank the transfer is a quarter of the step. The estimate
+// uses 600 GB/s for the broadcast and 3 POP/s for the GEMMs.
+int choose_layout(int m, int K, int N, int nm) {
     static const int forced = [] {
         const char *env = getenv("OZ_MG_LAYOUT");
         return !env ? -1 : !strcmp(env, "whole") ? LAYOUT_WHOLE : !strcmp(env, "stream") ? LAYOUT_STREAM : -1;
     }();
     if (forced >= 0) return forced;
-    return (size_t)K * N * 8 <= ((size_t)1 << 30) ? LAYOUT_WHOLE : LAYOUT_STREAM;
+    const double bytes = 8.0 * K * N, transfer = bytes / 600e9, compute = 2.0 * nm * m * (double)N * K / 3.0e15;
+    return bytes > (double)((size_t)1 << 30) && transfer > 0.08 * compute ? LAYOUT_STREAM : LAYOUT_WHOLE;
 }
 
 // C_local = A_local B on device operands; B is read on `root` only. Asynchronous on `st` (and the handle's own
@@ -201,7 +207,7 @@ int mg_dgemm_dev(ozb_mg *g, int m, int N, int K, const double *A, long long lda,
     const bool in_place = src && ldb == N;            // a dense B is sent from where it lies
     if (!in_place) if ((e = grow(&g->stageB, &g->stageB_elems, (size_t)K * N))) return (int)e;
     double *whole = in_place ? const_cast<double *>(B) : g->stageB;
-    const int layout = choose_layout(K, N);
+    const int layout = choose_layout(m, K, N, nm);
     // order: after the caller's writes of A and B (stream st), and after the previous product's reads of the staging copy
     if (src && !in_place) e = cudaMemcpy2DAsync(g->stageB, (size_t)N * 8, B, (size_t)ldb * 8, (size_t)N * 8, K, cudaMemcpyDeviceToDevice, st);
     if (!e) e = cudaMemsetAsync(p->colmax, 0, (size_t)N * 8, st);
@@ -230,11 +236,15 @@ int mg_dgemm_dev(ozb_mg *g, int m, int N, int K, const double *A, long long lda,
         // K ranges of the GEMMs: a first short one (the product starts early), then about 8192 each, on piece boundaries
         static const int kchunk = [] { const char *env = getenv("OZ_KCHUNK"); const int v = env && *env ? atoi(env) : 0; return v >= 1024 ? v : 8192; }();
         const int rows = piece_rows(K, N, target);
-        pieces = (K + rows - 1) / rows;
+        // the first piece is a quarter of the others: the first residues start that much earlier
+        const int first = rows >= 512 && K > rows ? rows / 4 / 128 * 128 : rows;
+        pieces = 1 + (K - first + rows - 1) / rows;
+        if (K <= first) pieces = 1;
         if (int c = mg_bcast(g, p->colmax, (size_t)N * 8, root)) return c;   // the column maxima, ahead of B on the same stream
         int range_k0 = 0, ranges = 0;
         for (int i = 0; i < pieces && !e; i++) {
-            const int k0 = i * rows, len = K - k0 < rows ? K - k0 : rows, done = k0 + len;
+            const int k0 = i == 0 ? 0 : first + (i - 1) * rows, full = i == 0 ? first : rows;
+            const int len = K - k0 < full ? K - k0 : full, done = k0 + len;
             if (int c = mg_bcast(g, whole + (size_t)k0 * N, (size_t)len * N * 8, root)) return c;
             if ((e = cudaEventRecord(g->evPiece[i], g->sComm))) break;
             if (!src) e = cudaStreamWaitEvent(st, g->evPiece[i], 0);

@@ -158,10 +158,10 @@ h = ctypes.c_void_p()
 g.check(lib.ozb_mg_create(2, rank, ident, 3000, ctypes.byref(h)))
 A, B = g.synthetic(M, K, 61), g.synthetic(K, N, 62)
 a = torch.from_numpy(A[rank * 128:(rank + 1) * 128].copy()).cuda()
-b = torch.from_numpy(B).cuda() if rank == 0 else None
+b = torch.from_numpy(B).cuda() if rank == 1 else None      # the rank that will leave holds B: the survivor is a receiver
 c = torch.zeros((128, N), dtype=torch.float64, device="cuda")
 bp = g.ptr(b) if b is not None else None
-g.check(lib.ozb_mg_dgemm(h, 128, N, K, g.ptr(a), K, bp, N, g.ptr(c), N, nm, 0, 0, None))
+g.check(lib.ozb_mg_dgemm(h, 128, N, K, g.ptr(a), K, bp, N, g.ptr(c), N, nm, 1, 0, None))
 g.check(lib.ozb_mg_wait(h))                      # one complete step on both ranks
 torch.cuda.synchronize()
 if rank == 1:
@@ -172,9 +172,9 @@ while not os.path.exists(os.path.join(out_dir, "left")):
     time.sleep(0.05)
 time.sleep(1.0)
 t0 = time.time()
-rc = lib.ozb_mg_dgemm(h, 128, N, K, g.ptr(a), K, bp, N, g.ptr(c), N, nm, 0, 0, None)
+rc = lib.ozb_mg_dgemm(h, 128, N, K, g.ptr(a), K, bp, N, g.ptr(c), N, nm, 1, 0, None)
 if rc == 0:
-    rc = lib.ozb_mg_wait(h)                      # the broadcast cannot complete: bounded wait, communicator aborted
+    rc = lib.ozb_mg_wait(h)                      # B never arrives: bounded wait, communicator aborted
 took = time.time() - t0
 again = lib.ozb_mg_wait(h)
 lib.ozb_mg_destroy(h)
@@ -185,7 +185,7 @@ open(os.path.join(out_dir, "rc"), "w").write(f"{rc} {again} {took:.2f}")
 
 
 def test_a_rank_that_leaves_between_steps_is_reported(tmp_path):
-    """Two ranks finish a step; rank 1 then exits. Rank 0's next product cannot complete its broadcast: the bounded host
+    """Two ranks finish a step; rank 1, which holds B, then exits. Rank 0's next product never receives B: the bounded host
     wait (3 s here) aborts the communicator and the call reports OZB_ECOMM instead of hanging; the handle stays broken and
     the CUDA context stays usable. Both ranks are child processes that are killed if they outlive the test's patience."""
     import subprocess
