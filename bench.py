@@ -392,7 +392,10 @@ class Bench:
                 op(A, B, C)
             ms_step = self.timed(step, steps, warm, sampler)
             op.engine.status()
-            launches = steps * (4 + len(op.ranges) if op.layout == "rows" else 2 + 4 * len(op.ranges))
+            if op.native:
+                launches = steps * op.native.kernels          # rank 0's kernels per product, counted by the library
+            else:
+                launches = steps * (4 + len(op.ranges) if op.layout == "rows" else 2 + 4 * len(op.ranges))
         clocks = sampler.stop() if rank == 0 else None
         flops_step = 2.0 * M * N * K * world
         value = flops_step / (ms_step * 1e-3) / 1e12

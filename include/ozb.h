@@ -168,9 +168,10 @@ int ozb_mg_dgemm(ozb_mg *g, int m_local, int N, int K, const double *A, long lon
 /* Waits (within the handle's budget) for the last product queued on the handle: 0, OZB_ETIMEOUT (a bounded wait inside a
  * GEMM kernel expired) or OZB_ECOMM. */
 int ozb_mg_wait(ozb_mg *g);
-/* How the last product moved B: *layout 0 = in one transfer, 1 = column maxima first, then pieces of rows consumed as
- * they land; *pieces = number of transfers of B. */
-int ozb_mg_info(ozb_mg *g, int *layout, int *pieces);
+/* How the last device-operand product moved B: *layout 0 = in one transfer, 1 = column maxima first, then pieces of rows
+ * consumed as they land; *pieces = number of transfers of B; *kernels = kernels of this library it launched on this rank
+ * (NCCL's own are not counted). Any pointer may be NULL. */
+int ozb_mg_info(ozb_mg *g, int *layout, int *pieces, int *kernels);
 
 /* bench/oz_strassen.cu:74-97,247 (scales_norm) -- C = A B with the reference's optional scaling from the 2-norm of each row
  * of A and column of B instead of its largest entry (Cauchy-Schwarz bounds the integer products without K, so more bits

@@ -73,7 +73,7 @@ lib.ozb_mg_destroy.restype = None
 lib.ozb_mg_destroy.argtypes = [_p]
 lib.ozb_mg_dgemm.argtypes = [_p, _i, _i, _i, _p, _ll, _p, _ll, _p, _ll, _i, _i, _i, _p]
 lib.ozb_mg_wait.argtypes = [_p]
-lib.ozb_mg_info.argtypes = [_p, _ip, _ip]
+lib.ozb_mg_info.argtypes = [_p, _ip, _ip, _ip]
 lib.ozb_status.argtypes = []
 lib.ozb_bounds_report.argtypes = [ctypes.POINTER(ctypes.c_ulonglong * 4)]
 lib.ozb_selftest_bounds.argtypes = []

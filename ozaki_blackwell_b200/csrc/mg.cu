@@ -95,7 +95,7 @@ struct ozb_mg {
     ozb_plan *plan;
     double *stageB; size_t stageB_elems;   // this rank's copy of B (receivers; a holder whose B is strided or comes from the host)
     double *dA, *dC; size_t dA_elems, dC_elems;   // host-operand and single-process paths: this rank's rows on its device
-    int last_layout, last_pieces;      // what the last product did (0 whole, 1 stream), for reports
+    int last_layout, last_pieces, last_kernels;   // what the last product did (0 whole, 1 stream; transfers of B; kernels of this library), for reports
 };
 
 namespace {
@@ -211,7 +211,8 @@ int mg_dgemm_dev(ozb_mg *g, int m, int N, int K, const double *A, long long lda,
     // order: after the caller's writes of A and B (stream st), and after the previous product's reads of the staging copy
     if (src && !in_place) e = cudaMemcpy2DAsync(g->stageB, (size_t)N * 8, B, (size_t)ldb * 8, (size_t)N * 8, K, cudaMemcpyDeviceToDevice, st);
     if (!e) e = cudaMemsetAsync(p->colmax, 0, (size_t)N * 8, st);
-    if (!e && layout == LAYOUT_STREAM && src) e = cols_absmax_accumulate(whole, K, N, N, p->colmax, st);
+    int kernels = 2;   // the residues of A and the reconstruction; counted below: maxima, residues of B, GEMM launches
+    if (!e && layout == LAYOUT_STREAM && src) { e = cols_absmax_accumulate(whole, K, N, N, p->colmax, st); kernels++; }
     if (!e) e = cudaEventRecord(g->evStart, st);
     if (!e) e = cudaStreamWaitEvent(g->sComm, g->evStart, 0);
     if (!e) e = cudaStreamWaitEvent(g->sComm, g->evDone, 0);
@@ -230,7 +231,8 @@ int mg_dgemm_dev(ozb_mg *g, int m, int N, int K, const double *A, long long lda,
         if (!src) e = cudaStreamWaitEvent(st, g->evPiece[0], 0);
         if (!e) e = cols_absmax_accumulate(whole, K, N, N, p->colmax, st);
         if (!e) e = cols_residues_from_max(nm, whole, K, N, N, p->bits, p->colmax, p->sb, p->Br, p->Kp, p->planeB, st);
-        if (!e) e = ozb_plan_gemm_range(p, N, 0, K, 0, st);
+        if (!e) e = ozb_plan_gemm_range(p, N, 0, K, 0, st, 0, -1, &kernels);
+        kernels += 2;
     } else {
         static const size_t target = [] { const char *env = getenv("OZ_MG_PIECE_MB"); const int v = env && *env ? atoi(env) : 0; return (size_t)(v > 0 ? v : 1024) << 20; }();
         // K ranges of the GEMMs: a first short one (the product starts early), then about 8192 each, on piece boundaries
@@ -249,15 +251,16 @@ int mg_dgemm_dev(ozb_mg *g, int m, int N, int K, const double *A, long long lda,
             if ((e = cudaEventRecord(g->evPiece[i], g->sComm))) break;
             if (!src) e = cudaStreamWaitEvent(st, g->evPiece[i], 0);
             if (!e) e = cols_residues_from_max(nm, whole + (size_t)k0 * N, len, N, N, p->bits, p->colmax, p->sb, p->Br + k0, p->Kp, p->planeB, st);
+            kernels++;
             const int want = ranges == 0 ? kchunk / 2 : kchunk;
             // close the range when it is long enough, unless what would remain is too short to be a range of its own
             if (!e && (i == pieces - 1 || (done - range_k0 >= want && K - done >= kchunk / 4))) {
-                e = ozb_plan_gemm_range(p, N, range_k0, done - range_k0, ranges > 0, st);
+                e = ozb_plan_gemm_range(p, N, range_k0, done - range_k0, ranges > 0, st, 0, -1, &kernels);
                 range_k0 = done; ranges++;
             }
         }
     }
-    g->last_layout = layout; g->last_pieces = pieces;
+    g->last_layout = layout; g->last_pieces = pieces; g->last_kernels = kernels;
     if (!e) e = crt_from_i8(nm, p->Cr, p->planeC, m, N, p->Np, p->sa, p->sb, C, ldc, st);
     // the holder's stream also waits for the sends: the caller may overwrite B (or the next call the staging copy) after this call
     if (!e && src) e = cudaStreamWaitEvent(st, g->evPiece[pieces - 1], 0);
@@ -446,10 +449,11 @@ OZB_API int ozb_mg_wait(ozb_mg *g) {
     return ozb_read_status_words(g->plan->status);
 }
 
-OZB_API int ozb_mg_info(ozb_mg *g, int *layout, int *pieces) {
+OZB_API int ozb_mg_info(ozb_mg *g, int *layout, int *pieces, int *kernels) {
     if (!g) return OZB_EARG;
     if (layout) *layout = g->last_layout;
     if (pieces) *pieces = g->last_pieces;
+    if (kernels) *kernels = g->last_kernels;
     return 0;
 }
 

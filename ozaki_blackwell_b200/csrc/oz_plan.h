@@ -38,5 +38,6 @@ int ozb_plan_make_internal(int M, int N, int K, int nm, int maxbits, ozb_plan **
 void ozb_plan_free_internal(ozb_plan *p);
 // the fused INT8 GEMMs of all planes over the inner range [k0, k0 + klen) of rows [i0, i0 + m) (m < 0: all rows) and the
 // first n columns; accumulate != 0 adds to the residues already in Cr (an earlier part of K)
-cudaError_t ozb_plan_gemm_range(ozb_plan *p, int n, int k0, int klen, int accumulate, cudaStream_t st, int i0 = 0, int m = -1);
+cudaError_t ozb_plan_gemm_range(ozb_plan *p, int n, int k0, int klen, int accumulate, cudaStream_t st, int i0 = 0, int m = -1,
+                                int *launches = nullptr);   // *launches is incremented per GEMM kernel launched
 int ozb_read_status_words(int *dev_words);

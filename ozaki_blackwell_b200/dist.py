@@ -170,7 +170,7 @@ class NativeSharded:
 
     def __init__(self, moduli, group=None, src=0, timeout_ms=0):
         from ._lib import lib
-        self._lib, self.moduli, self.src = lib, moduli, src
+        self._lib, self.moduli, self.src, self.kernels = lib, moduli, src, 0
         world, rank = dist.get_world_size(group), dist.get_rank(group)
         ident = ctypes.create_string_buffer(128)
         if rank == 0:
@@ -196,8 +196,9 @@ class NativeSharded:
         self._check(self._lib.ozb_mg_wait(self._handle))
 
     def info(self):
-        layout, pieces = ctypes.c_int(), ctypes.c_int()
-        self._check(self._lib.ozb_mg_info(self._handle, ctypes.byref(layout), ctypes.byref(pieces)))
+        layout, pieces, kernels = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+        self._check(self._lib.ozb_mg_info(self._handle, ctypes.byref(layout), ctypes.byref(pieces), ctypes.byref(kernels)))
+        self.kernels = kernels.value
         return ("whole", "stream")[layout.value], pieces.value
 
     def close(self):

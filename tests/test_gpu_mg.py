@@ -42,8 +42,9 @@ g.check(lib.ozb_mg_wait(h))
 got = Cd[:, :N].cpu().numpy()
 assert g.same_bits(got, want), g.describe_mismatch(got, want)
 assert torch.all(Cd[:, N:] == 7.0)
-layout, pieces = ctypes.c_int(), ctypes.c_int()
-g.check(lib.ozb_mg_info(h, ctypes.byref(layout), ctypes.byref(pieces)))
+layout, pieces, kernels = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+g.check(lib.ozb_mg_info(h, ctypes.byref(layout), ctypes.byref(pieces), ctypes.byref(kernels)))
+assert kernels.value >= 5
 print("layout", layout.value, "pieces", pieces.value)
 # a strided B is packed first
 Bw = torch.zeros((K, N + 5), dtype=torch.float64, device="cuda"); Bw[:, :N] = Bd
