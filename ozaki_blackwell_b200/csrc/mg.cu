@@ -8,14 +8,15 @@
 // exchanged, no kernel of the library reads another GPU's memory, and B is in the GPU's own HBM before any kernel or TMA
 // load touches it.
 //
-// How B travels depends on its size:
-//   whole   (B up to 1 GiB) one transfer straight out of the holder's matrix, beside the residues of A; then the column
+// How B travels depends on how long the transfer is against this rank's share of the product:
+//   whole   (a short transfer) one transfer straight out of the holder's matrix, beside the residues of A; then the column
 //           maxima, the residues of B, the GEMMs and the reconstruction, each once at full width.
-//   stream  (larger B) the holder first reduces the column maxima of its B (one pass at HBM speed) and sends those 8 N
-//           bytes ahead; B follows in pieces of whole rows (contiguous, nothing is packed). Every rank turns a piece into
-//           residues the moment it has landed and, as soon as the pieces of a K range of about 8192 are there, runs the
-//           INT8 GEMMs of that range at full width, adding to the residues of the ranges before it (the same cut of a
-//           long K the single-GPU product makes to keep its panels in L2). The reconstruction runs once at the end.
+//   stream  the holder first reduces the column maxima of its B (one pass at HBM speed) and sends those 8 N bytes ahead;
+//           B follows in pieces of whole rows (contiguous, nothing is packed; four to nine pieces). Every rank turns a
+//           piece into residues the moment it has landed. A K the single-GPU product runs in one launch then gets its one
+//           full-width GEMM launch after the last piece; a longer K gets the INT8 GEMMs of a K range of about 8192 as soon
+//           as the pieces of that range are there, adding to the residues of the ranges before it (the same cut of a long
+//           K the single-GPU product makes to keep its panels in L2). The reconstruction runs once at the end.
 //
 // NCCL is loaded at run time (dlopen of libnccl.so.2: the library itself links against nothing but the driver), the
 // communicator is non-blocking, and every host-side wait is bounded: when a call does not settle or a product does not
@@ -179,11 +180,11 @@ int piece_rows(int K, int N, size_t target) {
 }
 
 enum { LAYOUT_WHOLE = 0, LAYOUT_STREAM = 1 };
-// One transfer, or pieces consumed as they land? Streaming costs a pass over B on the holder before anything can be sent,
-// one more GEMM launch and NCCL's kernels beside the GEMMs; it pays when the transfer is long against this rank's share
-// of the product. Measured on B200s with n = 32768: two ranks (16384 rows each, 8 GiB of B) 216.1 ms in one transfer
-// against 222.9 - 225.1 ms in 4 - 8 pieces; with 4096 rows per rank the transfer is a quarter of the step. The estimate
-// uses 600 GB/s for the broadcast and 3 POP/s for the GEMMs.
+// One transfer, or pieces consumed as they land? Streaming costs a pass over B on the holder before anything can be sent
+// (the column maxima) and NCCL's kernels beside the compute kernels; it pays when the transfer is long against this
+// rank's share of the product. Measured on B200s with n = 32768: two ranks (16384 rows each, 8 GiB of B) 216.1 ms in one
+// transfer against 222.9 - 225.1 ms in 4 - 8 pieces; with 4096 rows per rank the transfer is a quarter of the step. The
+// estimate uses 600 GB/s for the broadcast and 3 POP/s for the GEMMs.
 int choose_layout(int m, int K, int N, int nm) {
     static const int forced = [] {
         const char *env = getenv("OZ_MG_LAYOUT");
@@ -191,7 +192,15 @@ int choose_layout(int m, int K, int N, int nm) {
     }();
     if (forced >= 0) return forced;
     const double bytes = 8.0 * K * N, transfer = bytes / 600e9, compute = 2.0 * nm * m * (double)N * K / 3.0e15;
-    return bytes > (double)((size_t)1 << 30) && transfer > 0.08 * compute ? LAYOUT_STREAM : LAYOUT_WHOLE;
+    return bytes >= (double)(64u << 20) && transfer > 0.08 * compute ? LAYOUT_STREAM : LAYOUT_WHOLE;
+}
+// bytes per piece of the stream layout: about 1 GiB, but at least four pieces (a B of 512 MiB travels in four pieces of
+// 128 MiB); many more outstanding transfers than eight were measured to cost more than they hide
+size_t piece_target(int K, int N) {
+    static const size_t forced = [] { const char *env = getenv("OZ_MG_PIECE_MB"); const int v = env && *env ? atoi(env) : 0; return (size_t)(v > 0 ? v : 0) << 20; }();
+    if (forced) return forced;
+    const size_t bytes = (size_t)K * N * 8, quarter = bytes / 4;
+    return quarter > ((size_t)1 << 30) ? (size_t)1 << 30 : quarter;
 }
 
 // C_local = A_local B on device operands; B is read on `root` only. Asynchronous on `st` (and the handle's own
@@ -234,12 +243,14 @@ int mg_dgemm_dev(ozb_mg *g, int m, int N, int K, const double *A, long long lda,
         if (!e) e = ozb_plan_gemm_range(p, N, 0, K, 0, st, 0, -1, &kernels);
         kernels += 2;
     } else {
-        static const size_t target = [] { const char *env = getenv("OZ_MG_PIECE_MB"); const int v = env && *env ? atoi(env) : 0; return (size_t)(v > 0 ? v : 1024) << 20; }();
-        // K ranges of the GEMMs: a first short one (the product starts early), then about 8192 each, on piece boundaries
+        // K ranges of the GEMMs, on piece boundaries. A K the single-GPU product runs in one launch (up to 1.5 chunks) stays
+        // one launch, after the last piece: only the residues of B are formed piece by piece. A longer K is cut as the
+        // single-GPU product cuts it: a first short range (the GEMMs start early), then about 8192 each.
         static const int kchunk = [] { const char *env = getenv("OZ_KCHUNK"); const int v = env && *env ? atoi(env) : 0; return v >= 1024 ? v : 8192; }();
-        const int rows = piece_rows(K, N, target);
-        // the first piece is a quarter of the others: the first residues start that much earlier
-        const int first = rows >= 512 && K > rows ? rows / 4 / 128 * 128 : rows;
+        const bool one_range = K <= kchunk + kchunk / 2;
+        const int rows = piece_rows(K, N, piece_target(K, N));
+        // with several ranges the first piece is a quarter of the others: the first residues start that much earlier
+        const int first = !one_range && rows >= 512 && K > rows ? rows / 4 / 128 * 128 : rows;
         pieces = 1 + (K - first + rows - 1) / rows;
         if (K <= first) pieces = 1;
         if (int c = mg_bcast(g, p->colmax, (size_t)N * 8, root)) return c;   // the column maxima, ahead of B on the same stream
@@ -254,7 +265,7 @@ int mg_dgemm_dev(ozb_mg *g, int m, int N, int K, const double *A, long long lda,
             kernels++;
             const int want = ranges == 0 ? kchunk / 2 : kchunk;
             // close the range when it is long enough, unless what would remain is too short to be a range of its own
-            if (!e && (i == pieces - 1 || (done - range_k0 >= want && K - done >= kchunk / 4))) {
+            if (!e && (i == pieces - 1 || (!one_range && done - range_k0 >= want && K - done >= kchunk / 4))) {
                 e = ozb_plan_gemm_range(p, N, range_k0, done - range_k0, ranges > 0, st, 0, -1, &kernels);
                 range_k0 = done; ranges++;
             }
