@@ -9,7 +9,7 @@
 // load touches it.
 //
 // How B travels depends on how long the transfer is against this rank's share of the product:
-//   whole   (a short transfer) one transfer straight out of the holder's matrix, beside the residues of A; then the column
+//   whole   (B up to 1 GiB, or a short transfer) one transfer straight out of the holder's matrix, beside the residues of A; then the column
 //           maxima, the residues of B, the GEMMs and the reconstruction, each once at full width.
 //   stream  the holder first reduces the column maxima of its B (one pass at HBM speed) and sends those 8 N bytes ahead;
 //           B follows in pieces of whole rows (contiguous, nothing is packed; four to nine pieces). Every rank turns a
@@ -183,7 +183,9 @@ enum { LAYOUT_WHOLE = 0, LAYOUT_STREAM = 1 };
 // One transfer, or pieces consumed as they land? Streaming costs a pass over B on the holder before anything can be sent
 // (the column maxima) and NCCL's kernels beside the compute kernels; it pays when the transfer is long against this
 // rank's share of the product. Measured on B200s with n = 32768: two ranks (16384 rows each, 8 GiB of B) 216.1 ms in one
-// transfer against 222.9 - 225.1 ms in 4 - 8 pieces; with 4096 rows per rank the transfer is a quarter of the step. The
+// transfer against 222.9 - 225.1 ms in 4 - 8 pieces; with 4096 rows per rank the transfer is a quarter of the step. A B of
+// 512 MiB (n = 8192) is always sent whole: two ranks 7.32 ms per product against 7.62 - 7.67 ms in 4 - 8 pieces (one GPU
+// 7.09 ms) -- NCCL's kernels beside the residue kernels cost more than the 0.25 ms of transfer they would hide. The
 // estimate uses 600 GB/s for the broadcast and 3 POP/s for the GEMMs.
 int choose_layout(int m, int K, int N, int nm) {
     static const int forced = [] {
@@ -192,7 +194,7 @@ int choose_layout(int m, int K, int N, int nm) {
     }();
     if (forced >= 0) return forced;
     const double bytes = 8.0 * K * N, transfer = bytes / 600e9, compute = 2.0 * nm * m * (double)N * K / 3.0e15;
-    return bytes >= (double)(64u << 20) && transfer > 0.08 * compute ? LAYOUT_STREAM : LAYOUT_WHOLE;
+    return bytes > (double)((size_t)1 << 30) && transfer > 0.08 * compute ? LAYOUT_STREAM : LAYOUT_WHOLE;
 }
 // bytes per piece of the stream layout: about 1 GiB, but at least four pieces (a B of 512 MiB travels in four pieces of
 // 128 MiB); many more outstanding transfers than eight were measured to cost more than they hide

@@ -35,6 +35,32 @@ def test_calls_that_need_no_device():
     assert lib.ozb_dgemm(4, 4, 131072, z, z, z, 16, 0) == 10002
 
 
+def test_multi_gpu_entry_points_check_their_arguments_first():
+    """The argument checks of the multi-GPU layer come before any device or NCCL work, as the reference's do
+    (python/capi.cu:23-29,79 for ozb_dgemm, whose shape ozb_dgemm_mg extends)."""
+    from ozaki_blackwell_b200._lib import lib
+    one = ctypes.c_void_p(16)                                         # never dereferenced
+    h = ctypes.c_void_p()
+    assert lib.ozb_dgemm_mg(0, 4, 4, one, one, one, 16, 1, 2) == 10001
+    assert lib.ozb_dgemm_mg(4, 4, 4, one, one, one, 7, 1, 2) == 10001
+    assert lib.ozb_dgemm_mg(4, 4, 4, one, one, one, 16, 1, 0) == 10001   # device count 1..16
+    assert lib.ozb_dgemm_mg(4, 4, 4, one, None, one, 16, 1, 2) == 10001
+    assert lib.ozb_dgemm_mg(4, 4, 131072, one, one, one, 16, 1, 2) == 10002
+    assert lib.ozb_mg_create(0, 0, one, 0, ctypes.byref(h)) == 10001
+    assert lib.ozb_mg_create(2, 2, one, 0, ctypes.byref(h)) == 10001     # rank outside the world
+    assert lib.ozb_mg_create(2, 0, None, 0, ctypes.byref(h)) == 10001    # more than one rank needs the rendezvous id
+    assert lib.ozb_mg_create(2, 0, one, -1, ctypes.byref(h)) == 10001
+    assert lib.ozb_mg_dgemm(None, 4, 4, 4, one, 4, one, 4, one, 4, 16, 0, 0, None) == 10001
+    assert lib.ozb_mg_wait(None) == 10001 and lib.ozb_mg_info(None, None, None, None) == 10001
+    lib.ozb_mg_destroy(None)                                             # tolerated
+    assert b"communicator" in lib.ozb_error(10007) and b"NCCL" in lib.ozb_error(10008)
+    ident = ctypes.create_string_buffer(128)
+    rc = lib.ozb_mg_unique_id(ident)                                     # needs libnccl.so.2, not a GPU
+    assert rc in (0, 10008)
+    assert rc != 0 or any(ident.raw)
+    assert lib.ozb_bounds_report(None) in (10001, 10005) and lib.ozb_selftest_bounds() in (10005, 35, 100, 10003)
+
+
 def test_cpp_header_compiles_as_plain_cxx(tmp_path):
     import subprocess
     src = tmp_path / "t.cpp"
