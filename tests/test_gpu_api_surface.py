@@ -44,6 +44,11 @@ def test_plan_interface_with_leading_dimensions_and_a_stream():
     g.check(lib.ozb_plan_phase_ms(plan, 0, ctypes.byref(ms)))
     assert ms[3] > 0 and abs(ms[0] + ms[1] + ms[2] - ms[3]) <= 0.05 * ms[3] + 0.02
     assert lib.ozb_plan_phase_ms(plan, 5, ctypes.byref(ms)) == 10001
+    km = (ctypes.c_float * 5)()                            # the same product kernel by kernel: the five parts add up to it
+    g.check(lib.ozb_plan_kernel_ms(plan, 0, ctypes.byref(km)))
+    assert all(t > 0 for t in km) and abs(sum(km) - ms[3]) <= 0.02 * ms[3] + 0.02
+    assert abs(km[0] + km[1] + km[2] - ms[0]) <= 0.02 and abs(km[3] - ms[1]) <= 0.02 and abs(km[4] - ms[2]) <= 0.02
+    assert lib.ozb_plan_kernel_ms(plan, 5, ctypes.byref(km)) == 10001
     # the split form: residues of A once, then two column panels
     Cd.fill_(0)
     g.check(lib.ozb_plan_set_a(plan, g.ptr(Ad), lda, None))

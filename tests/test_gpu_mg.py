@@ -244,6 +244,10 @@ for cur in (0, 1):
     g.check(lib.ozb_dgemm_mg(M, N, K, g.ptr(Ad), g.ptr(Bd), g.ptr(Cd), nm, 0, 2))
     assert g.same_bits(Cd.cpu().numpy(), want), cur
 assert lib.ozb_dgemm_mg(M, N, K, A.ctypes.data, B.ctypes.data, C.ctypes.data, nm, 1, 99) == 10001
+import ozaki_blackwell_b200 as ob
+assert g.same_bits(ob.matmul(A, B, moduli=nm, devices=2), want)          # the wrapper's keyword, host operands
+torch.cuda.set_device(0)
+assert g.same_bits(ob.matmul(g.dev(A), g.dev(B), moduli=nm, devices=2).cpu().numpy(), want)   # device operands
 lib.ozb_mg_release()
 print("ok")
 """, {"NCCL_NVLS_ENABLE": "0"})
