@@ -57,7 +57,8 @@ int ozb_ddgemm(int M, int N, int K, const double *Ah, const double *Al, const do
 int ozb_tdgemm(int M, int N, int K, const double *A0, const double *A1, const double *A2, const double *B0,
                const double *B1, const double *B2, double *C0, double *C1, double *C2, int on_host);
 
-/* python/capi.cu:124-127 -- free the cached plans (device memory); the next call plans again */
+/* python/capi.cu:124-127 -- free the cached plans (device memory); the next call plans again. Also frees what
+ * ozb_dgemm_mg keeps between calls (ozb_mg_release). */
 void ozb_release(void);
 
 /* python/capi.cu:130-164 -- GPU time of `reps` (1..101) products of fixed pseudo-random n x n matrices resident on the

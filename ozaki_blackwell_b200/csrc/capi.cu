@@ -531,6 +531,7 @@ OZB_API void ozb_release(void) {
     std::lock_guard<std::mutex> g(mu);
     for (Cache &c : cache) if (c.p) { plan_free(c.p); c.p = nullptr; }
     exact_f8_release();
+    ozb_mg_release();   // the communicators and workspaces ozb_dgemm_mg keeps between calls
 }
 
 static int bench_dd(int n, int reps, double *median_ms) {   // python/capi.cu:130-164, kind 1: lower parts 2^-53 below
