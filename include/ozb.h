@@ -169,6 +169,10 @@ int ozb_mg_dgemm(ozb_mg *g, int m_local, int N, int K, const double *A, long lon
 /* Waits (within the handle's budget) for the last product queued on the handle: 0, OZB_ETIMEOUT (a bounded wait inside a
  * GEMM kernel expired) or OZB_ECOMM. */
 int ozb_mg_wait(ozb_mg *g);
+/* What a device-operand product of this shape would do, without doing it (plain arithmetic, no device needed): *layout as
+ * in ozb_mg_info, *pieces = transfers of B, *ranges = K ranges whose GEMMs are launched as their pieces land (1: one launch
+ * after the last piece). Any pointer may be NULL. */
+int ozb_mg_schedule(int m_local, int N, int K, int moduli, int *layout, int *pieces, int *ranges);
 /* How the last device-operand product moved B: *layout 0 = in one transfer, 1 = column maxima first, then pieces of rows
  * consumed as they land; *pieces = number of transfers of B; *kernels = kernels of this library it launched on this rank
  * (NCCL's own are not counted). Any pointer may be NULL. */

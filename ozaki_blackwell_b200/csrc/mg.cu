@@ -126,12 +126,13 @@ int mg_bcast(ozb_mg *g, void *buf, size_t bytes, int root) {
     if (trace) fprintf(stderr, "ozb mg rank %d: broadcast of %zu bytes queued in %.3f ms (rc %d)\n", g->rank, bytes, ms_since(t0), rc);
     return rc;
 }
-// waits for an event on the host, within the budget, watching the communicator: a product whose broadcast never completes
-// (a peer is gone) ends here with the communicator aborted instead of blocking in a synchronise call for ever
-void drain(cudaEvent_t ev, int budget_ms) {   // after an abort the collective's kernel leaves and the stream drains; bounded all the same
+// after an abort the collective's kernel leaves and the stream drains; the wait for that is bounded all the same
+void drain(cudaEvent_t ev, int budget_ms) {
     const auto t0 = Clock::now();
     while (cudaEventQuery(ev) == cudaErrorNotReady && ms_since(t0) < budget_ms) std::this_thread::sleep_for(std::chrono::microseconds(200));
 }
+// waits for an event on the host, within the budget, watching the communicator: a product whose broadcast never completes
+// (a peer is gone) ends here with the communicator aborted instead of blocking in a synchronise call for ever
 int mg_wait_event(ozb_mg *g, cudaEvent_t ev) {
     const auto t0 = Clock::now();
     for (unsigned spin = 0;; spin++) {
@@ -205,6 +206,30 @@ size_t piece_target(int K, int N) {
     return quarter > ((size_t)1 << 30) ? (size_t)1 << 30 : quarter;
 }
 
+// The stream layout's schedule, as plain arithmetic: the pieces B travels in and, for each, whether the GEMMs of a K range
+// are launched behind it. A K the single-GPU product runs in one launch (up to 1.5 chunks) stays one launch, after the last
+// piece: only the residues of B are formed piece by piece. A longer K is cut as the single-GPU product cuts it: a first
+// short range (the GEMMs start early; its first piece is a quarter of the others), then about 8192 each.
+struct Piece { int k0, len, range_k0, range_len; };   // range_len > 0: the GEMMs of [range_k0, range_k0 + range_len) follow this piece
+int stream_schedule(int K, int N, Piece *out) {
+    static const int kchunk = [] { const char *env = getenv("OZ_KCHUNK"); const int v = env && *env ? atoi(env) : 0; return v >= 1024 ? v : 8192; }();
+    const bool one_range = K <= kchunk + kchunk / 2;
+    const int rows = piece_rows(K, N, piece_target(K, N));
+    const int first = !one_range && rows >= 512 && K > rows ? rows / 4 / 128 * 128 : rows;
+    const int pieces = K <= first ? 1 : 1 + (K - first + rows - 1) / rows;
+    int range_k0 = 0, ranges = 0;
+    for (int i = 0; i < pieces; i++) {
+        const int k0 = i == 0 ? 0 : first + (i - 1) * rows, full = i == 0 ? first : rows;
+        const int len = K - k0 < full ? K - k0 : full, done = k0 + len;
+        const int want = ranges == 0 ? kchunk / 2 : kchunk;
+        // close the range when it is long enough, unless what would remain is too short to be a range of its own
+        const bool close = i == pieces - 1 || (!one_range && done - range_k0 >= want && K - done >= kchunk / 4);
+        out[i] = Piece{k0, len, range_k0, close ? done - range_k0 : 0};
+        if (close) { range_k0 = done; ranges++; }
+    }
+    return pieces;
+}
+
 // C_local = A_local B on device operands; B is read on `root` only. Asynchronous on `st` (and the handle's own
 // communication stream); ozb_mg_wait reports how it ended.
 int mg_dgemm_dev(ozb_mg *g, int m, int N, int K, const double *A, long long lda, const double *B, long long ldb, double *C,
@@ -245,32 +270,17 @@ int mg_dgemm_dev(ozb_mg *g, int m, int N, int K, const double *A, long long lda,
         if (!e) e = ozb_plan_gemm_range(p, N, 0, K, 0, st, 0, -1, &kernels);
         kernels += 2;
     } else {
-        // K ranges of the GEMMs, on piece boundaries. A K the single-GPU product runs in one launch (up to 1.5 chunks) stays
-        // one launch, after the last piece: only the residues of B are formed piece by piece. A longer K is cut as the
-        // single-GPU product cuts it: a first short range (the GEMMs start early), then about 8192 each.
-        static const int kchunk = [] { const char *env = getenv("OZ_KCHUNK"); const int v = env && *env ? atoi(env) : 0; return v >= 1024 ? v : 8192; }();
-        const bool one_range = K <= kchunk + kchunk / 2;
-        const int rows = piece_rows(K, N, piece_target(K, N));
-        // with several ranges the first piece is a quarter of the others: the first residues start that much earlier
-        const int first = !one_range && rows >= 512 && K > rows ? rows / 4 / 128 * 128 : rows;
-        pieces = 1 + (K - first + rows - 1) / rows;
-        if (K <= first) pieces = 1;
+        Piece sched[MG_MAX_PIECES];
+        pieces = stream_schedule(K, N, sched);
         if (int c = mg_bcast(g, p->colmax, (size_t)N * 8, root)) return c;   // the column maxima, ahead of B on the same stream
-        int range_k0 = 0, ranges = 0;
-        for (int i = 0; i < pieces && !e; i++) {
-            const int k0 = i == 0 ? 0 : first + (i - 1) * rows, full = i == 0 ? first : rows;
-            const int len = K - k0 < full ? K - k0 : full, done = k0 + len;
-            if (int c = mg_bcast(g, whole + (size_t)k0 * N, (size_t)len * N * 8, root)) return c;
+        for (int i = 0, ranges = 0; i < pieces && !e; i++) {
+            const Piece &pc = sched[i];
+            if (int c = mg_bcast(g, whole + (size_t)pc.k0 * N, (size_t)pc.len * N * 8, root)) return c;
             if ((e = cudaEventRecord(g->evPiece[i], g->sComm))) break;
             if (!src) e = cudaStreamWaitEvent(st, g->evPiece[i], 0);
-            if (!e) e = cols_residues_from_max(nm, whole + (size_t)k0 * N, len, N, N, p->bits, p->colmax, p->sb, p->Br + k0, p->Kp, p->planeB, st);
+            if (!e) e = cols_residues_from_max(nm, whole + (size_t)pc.k0 * N, pc.len, N, N, p->bits, p->colmax, p->sb, p->Br + pc.k0, p->Kp, p->planeB, st);
             kernels++;
-            const int want = ranges == 0 ? kchunk / 2 : kchunk;
-            // close the range when it is long enough, unless what would remain is too short to be a range of its own
-            if (!e && (i == pieces - 1 || (!one_range && done - range_k0 >= want && K - done >= kchunk / 4))) {
-                e = ozb_plan_gemm_range(p, N, range_k0, done - range_k0, ranges > 0, st, 0, -1, &kernels);
-                range_k0 = done; ranges++;
-            }
+            if (!e && pc.range_len) e = ozb_plan_gemm_range(p, N, pc.range_k0, pc.range_len, ranges++ > 0, st, 0, -1, &kernels);
         }
     }
     g->last_layout = layout; g->last_pieces = pieces; g->last_kernels = kernels;
@@ -460,6 +470,23 @@ OZB_API int ozb_mg_wait(ozb_mg *g) {
     if (!g->plan) return 0;
     if (int c = mg_wait_event(g, g->evDone)) return c;
     return ozb_read_status_words(g->plan->status);
+}
+
+OZB_API int ozb_mg_schedule(int m_local, int N, int K, int moduli, int *layout, int *pieces, int *ranges) {
+    if (m_local <= 0 || N <= 0 || K <= 0 || moduli < 8 || moduli > 16) return OZB_EARG;
+    if (K >= 131072) return OZB_EK;
+    const int lay = choose_layout(m_local, K, N, moduli);
+    int np = 1, nr = 1;
+    if (lay == LAYOUT_STREAM) {
+        Piece sched[MG_MAX_PIECES];
+        np = stream_schedule(K, N, sched);
+        nr = 0;
+        for (int i = 0; i < np; i++) nr += sched[i].range_len > 0;
+    }
+    if (layout) *layout = lay;
+    if (pieces) *pieces = np;
+    if (ranges) *ranges = nr;
+    return 0;
 }
 
 OZB_API int ozb_mg_info(ozb_mg *g, int *layout, int *pieces, int *kernels) {

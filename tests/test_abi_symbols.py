@@ -61,6 +61,28 @@ def test_multi_gpu_entry_points_check_their_arguments_first():
     assert lib.ozb_bounds_report(None) in (10001, 10005) and lib.ozb_selftest_bounds() in (10005, 35, 100, 10003)
 
 
+def test_how_b_would_travel_is_plain_arithmetic():
+    """ozb_mg_schedule: what a sharded product of a given shape would do, without a device. B up to 1 GiB, or a transfer that
+    is short against the rank's share of the product, travels whole; the benchmark's large configuration (n = 32768 from four
+    ranks up) streams in nine pieces whose GEMMs are launched over five K ranges."""
+    from ozaki_blackwell_b200._lib import lib
+
+    def schedule(m, n, k, nm=16):
+        lay, pieces, ranges = ctypes.c_int(-1), ctypes.c_int(-1), ctypes.c_int(-1)
+        assert lib.ozb_mg_schedule(m, n, k, nm, ctypes.byref(lay), ctypes.byref(pieces), ctypes.byref(ranges)) == 0
+        return lay.value, pieces.value, ranges.value
+
+    assert schedule(8192, 8192, 8192) == (0, 1, 1)              # 512 MiB of B: one transfer
+    assert schedule(16384, 32768, 32768) == (0, 1, 1)           # two ranks: the transfer is short against 16384 rows
+    assert schedule(8192, 32768, 32768) == (1, 9, 5)            # four ranks
+    assert schedule(4096, 32768, 32768) == (1, 9, 5)            # eight ranks: 256 MiB first, then 1 GiB pieces
+    assert schedule(4096, 32768, 8192) == (1, 4, 1)             # a K of one launch keeps one GEMM launch
+    assert schedule(100, 500, 700) == (0, 1, 1)
+    assert lib.ozb_mg_schedule(0, 4, 4, 16, None, None, None) == 10001
+    assert lib.ozb_mg_schedule(4, 4, 131072, 16, None, None, None) == 10002
+    assert lib.ozb_mg_schedule(4, 4, 4, 16, None, None, None) == 0                 # NULL-tolerant
+
+
 def test_cpp_header_compiles_as_plain_cxx(tmp_path):
     import subprocess
     src = tmp_path / "t.cpp"
