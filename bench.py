@@ -500,7 +500,10 @@ class Bench:
 
         strong = None
         if args.strong_size > 0 and not args.strong:
-            strong = self.strong_case(args.strong_size, nm, args.strong_steps, 1)
+            try:
+                strong = self.strong_case(args.strong_size, nm, args.strong_steps, 1)
+            except Exception as exc:       # the headline line is still printed; the key then says what went wrong
+                strong = {"n": args.strong_size, "n_gpus": world, "error": f"{type(exc).__name__}: {exc}"[:300]}
 
         if rank == 0:
             line = {

@@ -151,7 +151,7 @@ static int plan_make(int M, int N, int K, int nm, int maxbits, ozb_plan **out) {
 // not (measured: 1.8 instead of 3.2 POP/s, the kernel turns HBM-bound); later chunks add to the residues the earlier ones
 // stored. `accumulate` says whether the first chunk already finds residues of an earlier part of K in Cr.
 static cudaError_t gemm_range(ozb_plan *p, const int8_t *Br, int8_t *Cr, int n, cudaStream_t st, int i0, int m, int k0, int klen,
-                              int accumulate, int *launches = nullptr) {
+                              int accumulate, int *launches = nullptr, int reserve_sms = 0) {
     if (m < 0) m = p->M;   // rows [i0, i0 + m) of A and C
     static const int target = [] { const char *env = getenv("OZ_KCHUNK"); const int v = env && *env ? atoi(env) : 0; return v >= 1024 ? v : 8192; }();
     const int chunks = klen > target + target / 2 ? (klen + target - 1) / target : 1;
@@ -159,7 +159,7 @@ static cudaError_t gemm_range(ozb_plan *p, const int8_t *Br, int8_t *Cr, int n, 
     for (int k = k0, i = 0; k < k0 + klen; k += kc, i++) {
         const int len = k0 + klen - k < kc ? k0 + klen - k : kc;
         cudaError_t e = gemm_i8_planes(p->Ar + (size_t)i0 * p->Kp + k, Br + k, Cr + (size_t)i0 * p->Np, m, n, len, p->nm, p->Kp, p->Kp,
-                                       p->Np, p->planeA, p->planeB, p->planeC, 1, 0, p->status, 0, st, accumulate || i > 0);
+                                       p->Np, p->planeA, p->planeB, p->planeC, 1, 0, p->status, 0, st, accumulate || i > 0, reserve_sms);
         if (e) return e;
         if (launches) ++*launches;
     }
@@ -168,8 +168,9 @@ static cudaError_t gemm_range(ozb_plan *p, const int8_t *Br, int8_t *Cr, int n, 
 static cudaError_t gemm_chunks(ozb_plan *p, const int8_t *Br, int8_t *Cr, int n, cudaStream_t st, int i0 = 0, int m = -1) {
     return gemm_range(p, Br, Cr, n, st, i0, m, 0, p->K, 0);
 }
-cudaError_t ozb_plan_gemm_range(ozb_plan *p, int n, int k0, int klen, int accumulate, cudaStream_t st, int i0, int m, int *launches) {
-    return gemm_range(p, p->Br, p->Cr, n, st, i0, m, k0, klen, accumulate, launches);
+cudaError_t ozb_plan_gemm_range(ozb_plan *p, int n, int k0, int klen, int accumulate, cudaStream_t st, int i0, int m, int *launches,
+                                int reserve_sms) {
+    return gemm_range(p, p->Br, p->Cr, n, st, i0, m, k0, klen, accumulate, launches, reserve_sms);
 }
 
 // a plan's workspaces live on the device that was current when it was made: launching from another one would read them

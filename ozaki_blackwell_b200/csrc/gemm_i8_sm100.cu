@@ -736,9 +736,11 @@ static int *next_work_counter() {
 // plane z mod modulus(first_modulus + z); ldc must then be a multiple of 16 with the padding columns writable.
 // `status` is a device int the kernel sets if a barrier wait expired. `sms` = 0 uses every SM. accumulate = 1 (fused mode only)
 // adds the residues already in C before reducing: the caller splits a long K into chunks whose panels stay in L2.
+// `reserve_sms` SMs are left free: a persistent grid never gives an SM back before the launch ends, so a kernel that must
+// start while this one runs (the next transfer of a broadcast in flight) needs SMs that this launch does not take.
 cudaError_t gemm_i8_planes(const int8_t *A, const int8_t *Bt, void *C, int M, int N, int K, int Z, long long lda, long long ldb,
                            long long ldc, size_t pa, size_t pb, size_t pc, int fused, int first_modulus, int *status, int sms,
-                           cudaStream_t st, int accumulate) {
+                           cudaStream_t st, int accumulate, int reserve_sms) {
     if (M <= 0 || N <= 0 || K <= 0 || Z <= 0 || (accumulate && !fused)) return cudaErrorInvalidValue;
     if (fused && ((ldc & 15) || first_modulus < 0 || first_modulus + Z > MAXM)) return cudaErrorInvalidValue;
     cudaError_t e = gemm_setup();
@@ -795,7 +797,8 @@ cudaError_t gemm_i8_planes(const int8_t *A, const int8_t *Bt, void *C, int M, in
             if (getenv("OZ_DEBUG")) fprintf(stderr, "ozb: %d SMs, at most %d resident CTA pairs\n", sms, n);
         }
         const long long pairs_total = (long long)((M + g8::two::BM2 - 1) / g8::two::BM2) * p.tiles_n * Z;
-        const int limit = mp[fused ? 1 : 0];
+        int limit = mp[fused ? 1 : 0] - (reserve_sms > 0 ? (reserve_sms + 1) / 2 : 0);
+        if (limit < 1) limit = 1;
         const int pairs = (int)(pairs_total < limit ? pairs_total : limit);
         if (!(p.counter = next_work_counter())) return cudaErrorInvalidDevice;
         if ((e = cudaMemsetAsync(p.counter, 0, sizeof(int), st))) return e;
@@ -803,6 +806,7 @@ cudaError_t gemm_i8_planes(const int8_t *A, const int8_t *Bt, void *C, int M, in
         else g8::gemm_i8_tc2<false><<<2 * pairs, g8::THREADS, g8::two::SMEM2_BYTES, st>>>(mapA, mapB, p);
         return cudaGetLastError();
     }
+    if (reserve_sms > 0 && sms - reserve_sms >= 1) sms -= reserve_sms;
     const int grid = (int)(total < sms ? total : sms);
     if (fused) g8::gemm_i8_tc<true><<<grid, g8::THREADS, g8::SMEM_BYTES, st>>>(mapA, mapB, p);
     else g8::gemm_i8_tc<false><<<grid, g8::THREADS, g8::SMEM_BYTES, st>>>(mapA, mapB, p);

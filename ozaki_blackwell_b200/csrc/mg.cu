@@ -24,10 +24,12 @@
 // handle is marked broken and the call returns OZB_ECOMM; the CUDA context stays usable.
 #include <nccl.h>
 #include <dlfcn.h>
+#include <atomic>
 #include <chrono>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <memory>
 #include <mutex>
 #include <thread>
 #include "../../include/ozb.h"
@@ -89,40 +91,58 @@ double ms_since(Clock::time_point t0) { return std::chrono::duration<double, std
 constexpr int MG_MAX_PIECES = 64, MG_MAX_BLOCKS = 32;
 struct ozb_mg {
     int world, rank, dev, timeout_ms;
-    ncclComm_t comm;
+    int reserve_sms;                   // SMs the GEMMs leave to NCCL's kernels while transfers are outstanding (its CTA cap)
+    ncclComm_t comm;                   // every transfer that is waited for: as many CTAs as NCCL likes
+    ncclComm_t comm_beside;            // transfers that run beside the GEMMs (the stream layout): CTAs capped, SMs reserved for them
     bool broken;                       // the communicator was aborted: every later call answers OZB_ECOMM
     cudaStream_t sComm, sIn, sRun, sOut;
     cudaEvent_t evStart, evDone, evPiece[MG_MAX_PIECES], evIn[MG_MAX_PIECES], evRun[MG_MAX_BLOCKS];
     ozb_plan *plan;
     double *stageB; size_t stageB_elems;   // this rank's copy of B (receivers; a holder whose B is strided or comes from the host)
     double *dA, *dC; size_t dA_elems, dC_elems;   // host-operand and single-process paths: this rank's rows on its device
+    cudaEvent_t mark[96]; char mark_name[96][20]; int marks;   // OZ_MG_TRACE: a timeline of the last product on this rank
     int last_layout, last_pieces, last_kernels;   // what the last product did (0 whole, 1 stream; transfers of B; kernels of this library), for reports
 };
 
 namespace {
 
+// ncclCommAbort of the handle's communicators, side by side and bounded: each runs in a thread of its own, and a thread
+// that has not come back within the budget (a tear-down that waits for a peer that is gone) is left behind rather than
+// waited for -- the call that noticed the failure must return.
+void abort_comms(ncclComm_t a, ncclComm_t b, int budget_ms) {
+    std::shared_ptr<std::atomic<int>> left = std::make_shared<std::atomic<int>>(0);
+    for (ncclComm_t c : {a, b}) {
+        if (!c) continue;
+        left->fetch_add(1);
+        std::thread([c, left] { nccl().CommAbort(c); left->fetch_sub(1); }).detach();
+    }
+    const auto t0 = Clock::now();
+    while (left->load() > 0 && ms_since(t0) < budget_ms) std::this_thread::sleep_for(std::chrono::microseconds(200));
+}
 void mg_abort(ozb_mg *g) {
-    if (g->comm && !g->broken) nccl().CommAbort(g->comm);
-    g->comm = nullptr;
+    if (!g->broken) abort_comms(g->comm, g->comm_beside != g->comm ? g->comm_beside : nullptr, g->timeout_ms);
+    g->comm = g->comm_beside = nullptr;
     g->broken = true;
 }
 // waits, within the handle's budget, until the communicator has settled the call that returned `r`
-int mg_settle(ozb_mg *g, ncclResult_t r) {
+int mg_settle(ozb_mg *g, ncclResult_t r, ncclComm_t comm = nullptr) {
+    if (!comm) comm = g->comm;
     const auto t0 = Clock::now();
     while (r == ncclInProgress) {
         if (ms_since(t0) > g->timeout_ms) { mg_abort(g); return OZB_ECOMM; }
         std::this_thread::sleep_for(std::chrono::microseconds(20));
-        if (nccl().CommGetAsyncError(g->comm, &r) != ncclSuccess) { mg_abort(g); return OZB_ECOMM; }
+        if (nccl().CommGetAsyncError(comm, &r) != ncclSuccess) { mg_abort(g); return OZB_ECOMM; }
     }
     if (r != ncclSuccess) { mg_abort(g); return OZB_ECOMM; }
     return 0;
 }
-int mg_bcast(ozb_mg *g, void *buf, size_t bytes, int root) {
+int mg_bcast(ozb_mg *g, void *buf, size_t bytes, int root, bool beside = false) {
     if (g->world == 1) return 0;   // a single rank holds B already; the rest of the schedule is the same
     if (g->broken) return OZB_ECOMM;
     static const bool trace = getenv("OZ_MG_TRACE") != nullptr;   // host time of every enqueue, on stderr
     const auto t0 = Clock::now();
-    const int rc = mg_settle(g, nccl().Broadcast(buf, buf, bytes, ncclChar, root, g->comm, g->sComm));
+    ncclComm_t comm = beside ? g->comm_beside : g->comm;
+    const int rc = mg_settle(g, nccl().Broadcast(buf, buf, bytes, ncclChar, root, comm, g->sComm), comm);
     if (trace) fprintf(stderr, "ozb mg rank %d: broadcast of %zu bytes queued in %.3f ms (rc %d)\n", g->rank, bytes, ms_since(t0), rc);
     return rc;
 }
@@ -141,7 +161,10 @@ int mg_wait_event(ozb_mg *g, cudaEvent_t ev) {
         if (q != cudaErrorNotReady) return (int)q;
         if ((spin & 63) == 63 && g->comm) {
             ncclResult_t r = ncclSuccess;
-            if (nccl().CommGetAsyncError(g->comm, &r) != ncclSuccess || (r != ncclSuccess && r != ncclInProgress)) {
+            ncclResult_t r2 = ncclSuccess;
+            const bool bad2 = g->comm_beside && g->comm_beside != g->comm &&
+                              (nccl().CommGetAsyncError(g->comm_beside, &r2) != ncclSuccess || (r2 != ncclSuccess && r2 != ncclInProgress));
+            if (bad2 || nccl().CommGetAsyncError(g->comm, &r) != ncclSuccess || (r != ncclSuccess && r != ncclInProgress)) {
                 mg_abort(g);
                 drain(ev, g->timeout_ms);
                 return OZB_ECOMM;
@@ -209,25 +232,50 @@ size_t piece_target(int K, int N) {
 // The stream layout's schedule, as plain arithmetic: the pieces B travels in and, for each, whether the GEMMs of a K range
 // are launched behind it. A K the single-GPU product runs in one launch (up to 1.5 chunks) stays one launch, after the last
 // piece: only the residues of B are formed piece by piece. A longer K is cut as the single-GPU product cuts it: a first
-// short range (the GEMMs start early; its first piece is a quarter of the others), then about 8192 each.
+// short range of about 2048 (one piece of half the usual size: the GEMMs start early), a second of about 4096, then about
+// 8192 each; arrival (about 240 GB/s with NCCL's capped kernels) stays ahead of the GEMMs from there on.
 struct Piece { int k0, len, range_k0, range_len; };   // range_len > 0: the GEMMs of [range_k0, range_k0 + range_len) follow this piece
 int stream_schedule(int K, int N, Piece *out) {
     static const int kchunk = [] { const char *env = getenv("OZ_KCHUNK"); const int v = env && *env ? atoi(env) : 0; return v >= 1024 ? v : 8192; }();
     const bool one_range = K <= kchunk + kchunk / 2;
     const int rows = piece_rows(K, N, piece_target(K, N));
-    const int first = !one_range && rows >= 512 && K > rows ? rows / 4 / 128 * 128 : rows;
+    const int first = !one_range && rows >= 512 && K > rows ? rows / 2 / 128 * 128 : rows;
     const int pieces = K <= first ? 1 : 1 + (K - first + rows - 1) / rows;
     int range_k0 = 0, ranges = 0;
     for (int i = 0; i < pieces; i++) {
         const int k0 = i == 0 ? 0 : first + (i - 1) * rows, full = i == 0 ? first : rows;
         const int len = K - k0 < full ? K - k0 : full, done = k0 + len;
-        const int want = ranges == 0 ? kchunk / 2 : kchunk;
-        // close the range when it is long enough, unless what would remain is too short to be a range of its own
-        const bool close = i == pieces - 1 || (!one_range && done - range_k0 >= want && K - done >= kchunk / 4);
+        const int want = ranges == 0 ? kchunk / 4 : ranges == 1 ? kchunk / 2 : kchunk;
+        // close the range when it is long enough, unless what would remain is too short to be a range of its own (a short K
+        // leaves the accumulating epilogue, which re-reads the residues of the ranges before, longer than the MMAs of a tile)
+        const bool close = i == pieces - 1 || (!one_range && done - range_k0 >= want && K - done >= kchunk * 3 / 4);
         out[i] = Piece{k0, len, range_k0, close ? done - range_k0 : 0};
         if (close) { range_k0 = done; ranges++; }
     }
     return pieces;
+}
+
+// OZ_MG_TRACE: a timing mark on the compute stream (events are created on first use and kept with the handle)
+void mg_mark(ozb_mg *g, cudaStream_t st, const char *name, int i = -1) {
+    static const bool trace = getenv("OZ_MG_TRACE") != nullptr;
+    if (!trace || g->marks >= 96) return;
+    cudaEvent_t &ev = g->mark[g->marks];
+    if (!ev && cudaEventCreate(&ev) != cudaSuccess) return;
+    if (i >= 0) snprintf(g->mark_name[g->marks], sizeof g->mark_name[0], "%s%d", name, i);
+    else snprintf(g->mark_name[g->marks], sizeof g->mark_name[0], "%s", name);
+    cudaEventRecord(ev, st);
+    g->marks++;
+}
+void mg_print_marks(ozb_mg *g) {
+    if (g->marks < 2) return;
+    fprintf(stderr, "ozb mg rank %d timeline (ms):", g->rank);
+    for (int i = 1; i < g->marks; i++) {
+        float t = 0;
+        if (cudaEventElapsedTime(&t, g->mark[i - 1], g->mark[i]) == cudaSuccess) fprintf(stderr, " %s %.2f", g->mark_name[i], t);
+    }
+    float all = 0;
+    cudaEventElapsedTime(&all, g->mark[0], g->mark[g->marks - 1]);
+    fprintf(stderr, " | total %.2f\n", all);
 }
 
 // C_local = A_local B on device operands; B is read on `root` only. Asynchronous on `st` (and the handle's own
@@ -247,6 +295,8 @@ int mg_dgemm_dev(ozb_mg *g, int m, int N, int K, const double *A, long long lda,
     // order: after the caller's writes of A and B (stream st), and after the previous product's reads of the staging copy
     if (src && !in_place) e = cudaMemcpy2DAsync(g->stageB, (size_t)N * 8, B, (size_t)ldb * 8, (size_t)N * 8, K, cudaMemcpyDeviceToDevice, st);
     if (!e) e = cudaMemsetAsync(p->colmax, 0, (size_t)N * 8, st);
+    g->marks = 0;
+    mg_mark(g, st, "start");
     int kernels = 2;   // the residues of A and the reconstruction; counted below: maxima, residues of B, GEMM launches
     if (!e && layout == LAYOUT_STREAM && src) { e = cols_absmax_accumulate(whole, K, N, N, p->colmax, st); kernels++; }
     if (!e) e = cudaEventRecord(g->evStart, st);
@@ -258,33 +308,48 @@ int mg_dgemm_dev(ozb_mg *g, int m, int N, int K, const double *A, long long lda,
     // consumes the piece (the compute stream waits for the arrival on the device). Queueing every transfer before any
     // computation would leave the GPU without work while the host is still inside NCCL's enqueue calls, which take
     // milliseconds each when several transfers are outstanding.
+    mg_mark(g, st, "maxima");
     e = scale_residues_rows(nm, A, m, K, lda, p->bits, p->sa, p->Ar, p->Kp, p->planeA, st);
     if (e) return (int)e;
+    mg_mark(g, st, "rowsA");
     int pieces = 1;
     if (layout == LAYOUT_WHOLE) {
         if (int c = mg_bcast(g, whole, (size_t)K * N * 8, root)) return c;
         if ((e = cudaEventRecord(g->evPiece[0], g->sComm))) return (int)e;
         if (!src) e = cudaStreamWaitEvent(st, g->evPiece[0], 0);
+        mg_mark(g, st, "wait");
         if (!e) e = cols_absmax_accumulate(whole, K, N, N, p->colmax, st);
         if (!e) e = cols_residues_from_max(nm, whole, K, N, N, p->bits, p->colmax, p->sb, p->Br, p->Kp, p->planeB, st);
+        mg_mark(g, st, "colsB");
         if (!e) e = ozb_plan_gemm_range(p, N, 0, K, 0, st, 0, -1, &kernels);
+        mg_mark(g, st, "gemm");
         kernels += 2;
     } else {
         Piece sched[MG_MAX_PIECES];
         pieces = stream_schedule(K, N, sched);
-        if (int c = mg_bcast(g, p->colmax, (size_t)N * 8, root)) return c;   // the column maxima, ahead of B on the same stream
+        if (int c = mg_bcast(g, p->colmax, (size_t)N * 8, root, true)) return c;   // the column maxima, ahead of B on the same stream
         for (int i = 0, ranges = 0; i < pieces && !e; i++) {
             const Piece &pc = sched[i];
-            if (int c = mg_bcast(g, whole + (size_t)pc.k0 * N, (size_t)pc.len * N * 8, root)) return c;
+            if (int c = mg_bcast(g, whole + (size_t)pc.k0 * N, (size_t)pc.len * N * 8, root, true)) return c;
             if ((e = cudaEventRecord(g->evPiece[i], g->sComm))) break;
             if (!src) e = cudaStreamWaitEvent(st, g->evPiece[i], 0);
+            mg_mark(g, st, "wait", i);
             if (!e) e = cols_residues_from_max(nm, whole + (size_t)pc.k0 * N, pc.len, N, N, p->bits, p->colmax, p->sb, p->Br + pc.k0, p->Kp, p->planeB, st);
             kernels++;
-            if (!e && pc.range_len) e = ozb_plan_gemm_range(p, N, pc.range_k0, pc.range_len, ranges++ > 0, st, 0, -1, &kernels);
+            mg_mark(g, st, "res", i);
+            if (!e && pc.range_len) {
+                // A persistent GEMM gives no SM back before it ends, and the transfer of the next piece is a kernel of its
+                // own that starts when the one before it has finished: while pieces are still to come, the GEMMs leave
+                // NCCL's SMs free (the last range starts after the last piece has landed and takes them all).
+                const int reserve = g->world > 1 && i < pieces - 1 ? g->reserve_sms : 0;
+                e = ozb_plan_gemm_range(p, N, pc.range_k0, pc.range_len, ranges++ > 0, st, 0, -1, &kernels, reserve);
+                mg_mark(g, st, "gemm", ranges - 1);
+            }
         }
     }
     g->last_layout = layout; g->last_pieces = pieces; g->last_kernels = kernels;
     if (!e) e = crt_from_i8(nm, p->Cr, p->planeC, m, N, p->Np, p->sa, p->sb, C, ldc, st);
+    mg_mark(g, st, "crt");
     // the holder's stream also waits for the sends: the caller may overwrite B (or the next call the staging copy) after this call
     if (!e && src) e = cudaStreamWaitEvent(st, g->evPiece[pieces - 1], 0);
     if (!e) e = cudaEventRecord(g->evDone, st);
@@ -410,13 +475,54 @@ OZB_API int ozb_mg_create(int world, int rank, const void *id, int timeout_ms, o
         memcpy(&u, id, sizeof u);
         ncclConfig_t cfg = NCCL_CONFIG_INITIALIZER;
         cfg.blocking = 0;
-        const char *env = getenv("OZ_MG_MAX_CTAS");   // SMs NCCL's kernels may hold while they run beside the GEMMs
-        if (env && atoi(env) > 0) cfg.maxCTAs = atoi(env);
         rc = mg_settle(g, nccl().CommInitRankConfig(&g->comm, world, u, rank, &cfg));
         if (!rc) {   // initialisation itself proceeds in the background: wait for it within the budget
             ncclResult_t r = ncclInProgress;
             if (nccl().CommGetAsyncError(g->comm, &r) != ncclSuccess) r = ncclInternalError;
             rc = mg_settle(g, r);
+        }
+        // A second communicator over the same ranks for the transfers that run beside the GEMMs: its kernels are capped to a
+        // few CTAs (OZ_MG_MAX_CTAS, default 16) and the GEMMs leave as many SMs free (OZ_MG_RESERVE_SMS). Transfers that are
+        // waited for keep the first communicator and all the CTAs NCCL wants: capped, a 512 MiB broadcast between four
+        // B200s took 0.9 ms longer.
+        g->comm_beside = g->comm;
+        g->reserve_sms = 0;
+        static const bool two = [] { const char *env = getenv("OZ_MG_ONE_COMM"); return !(env && *env == '1'); }();
+        if (!rc && two) {
+            // its rendezvous id is made by rank 0 and travels over the first communicator
+            ncclUniqueId u2;
+            void *dbuf = nullptr;
+            cudaError_t ce = cudaMalloc(&dbuf, sizeof u2);
+            if (!ce && rank == 0) {
+                if (nccl().GetUniqueId(&u2) != ncclSuccess) ce = cudaErrorUnknown;
+                if (!ce) ce = cudaMemcpyAsync(dbuf, &u2, sizeof u2, cudaMemcpyHostToDevice, g->sComm);
+            }
+            if (ce) rc = (int)ce;
+            if (!rc) rc = mg_bcast(g, dbuf, sizeof u2, 0);
+            if (!rc) rc = (int)cudaEventRecord(g->evStart, g->sComm);
+            if (!rc) rc = mg_wait_event(g, g->evStart);
+            if (!rc) rc = (int)cudaMemcpy(&u2, dbuf, sizeof u2, cudaMemcpyDeviceToHost);
+            cudaFree(dbuf);
+            if (!rc) {
+                ncclConfig_t cap = NCCL_CONFIG_INITIALIZER;
+                cap.blocking = 0;
+                const char *env = getenv("OZ_MG_MAX_CTAS");
+                cap.maxCTAs = env && atoi(env) > 0 ? atoi(env) : 16;
+                ncclComm_t second = nullptr;
+                ncclResult_t r = nccl().CommInitRankConfig(&second, world, u2, rank, &cap);
+                if (second) g->comm_beside = second;          // from here on an abort takes it along
+                if (r == ncclInProgress || r == ncclSuccess) {
+                    ncclResult_t st2 = ncclInProgress;
+                    if (!second || nccl().CommGetAsyncError(second, &st2) != ncclSuccess) st2 = ncclInternalError;
+                    rc = mg_settle(g, st2, second);
+                } else {
+                    rc = mg_settle(g, r, second);
+                }
+                if (!rc) {
+                    const char *res = getenv("OZ_MG_RESERVE_SMS");
+                    g->reserve_sms = res && *res ? atoi(res) : cap.maxCTAs;
+                }
+            }
         }
     }
     if (rc) { ozb_mg_destroy(g); return rc; }
@@ -436,7 +542,7 @@ OZB_API void ozb_mg_destroy(ozb_mg *g) {
         // handle's own transfers have been waited for by then (every product ends with ozb_mg_wait or a synchronous call).
         cudaEvent_t idle = g->evStart;
         if (cudaEventRecord(idle, g->sComm) == cudaSuccess) drain(idle, g->timeout_ms);
-        nccl().CommAbort(g->comm);
+        abort_comms(g->comm, g->comm_beside != g->comm ? g->comm_beside : nullptr, g->timeout_ms);
     }
     if (g->plan) ozb_plan_free_internal(g->plan);
     cudaFree(g->stageB); cudaFree(g->dA); cudaFree(g->dC);
@@ -445,6 +551,7 @@ OZB_API void ozb_mg_destroy(ozb_mg *g) {
     for (auto ev : g->evPiece) if (ev) cudaEventDestroy(ev);
     for (auto ev : g->evIn) if (ev) cudaEventDestroy(ev);
     for (auto ev : g->evRun) if (ev) cudaEventDestroy(ev);
+    for (auto ev : g->mark) if (ev) cudaEventDestroy(ev);
     delete g;
     if (cur >= 0 && cur != dev) cudaSetDevice(cur);
 }
@@ -469,6 +576,7 @@ OZB_API int ozb_mg_wait(ozb_mg *g) {
     if (g->broken) return OZB_ECOMM;
     if (!g->plan) return 0;
     if (int c = mg_wait_event(g, g->evDone)) return c;
+    mg_print_marks(g);
     return ozb_read_status_words(g->plan->status);
 }
 

@@ -39,5 +39,6 @@ void ozb_plan_free_internal(ozb_plan *p);
 // the fused INT8 GEMMs of all planes over the inner range [k0, k0 + klen) of rows [i0, i0 + m) (m < 0: all rows) and the
 // first n columns; accumulate != 0 adds to the residues already in Cr (an earlier part of K)
 cudaError_t ozb_plan_gemm_range(ozb_plan *p, int n, int k0, int klen, int accumulate, cudaStream_t st, int i0 = 0, int m = -1,
-                                int *launches = nullptr);   // *launches is incremented per GEMM kernel launched
+                                int *launches = nullptr,    // *launches is incremented per GEMM kernel launched
+                                int reserve_sms = 0);       // SMs the launches leave free for kernels that must start beside them
 int ozb_read_status_words(int *dev_words);

@@ -75,7 +75,7 @@ def test_how_b_would_travel_is_plain_arithmetic():
     assert schedule(8192, 8192, 8192) == (0, 1, 1)              # 512 MiB of B: one transfer
     assert schedule(16384, 32768, 32768) == (0, 1, 1)           # two ranks: the transfer is short against 16384 rows
     assert schedule(8192, 32768, 32768) == (1, 9, 5)            # four ranks
-    assert schedule(4096, 32768, 32768) == (1, 9, 5)            # eight ranks: 256 MiB first, then 1 GiB pieces
+    assert schedule(4096, 32768, 32768) == (1, 9, 5)            # eight ranks: 512 MiB first, then 1 GiB pieces
     assert schedule(4096, 32768, 8192) == (1, 4, 1)             # a K of one launch keeps one GEMM launch
     assert schedule(100, 500, 700) == (0, 1, 1)
     assert lib.ozb_mg_schedule(0, 4, 4, 16, None, None, None) == 10001
