@@ -605,11 +605,20 @@ class Bench:
         for _ in range(steps):
             e2e_step()
         self.barrier()
-        dt = self.max_over_ranks((time.perf_counter() - t0) / steps)
+        own = (time.perf_counter() - t0) / steps
+        dt = self.max_over_ranks(own)
+        # each rank's own time per step, without the closing barrier of the other ranks: shows which rank the host link holds up
+        t1 = time.perf_counter()
+        e2e_step()
+        alone = torch.tensor([(time.perf_counter() - t1) * 1e3], dtype=torch.float64, device=dev)
+        per_rank = [alone.clone() for _ in range(world)]
+        if world > 1:
+            self.dist.all_gather(per_rank, alone)
         if not torch.equal(Ch.to(dev), C):
             raise RuntimeError(f"rank {rank}: the host-staged result differs from the device-resident result")
         return {"value": flops_step / dt / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": dt * 1e3, "steps": steps, "how": how}
+                "ms_per_step": dt * 1e3, "steps": steps, "ms_last_step_per_rank": [round(float(t.item()), 3) for t in per_rank],
+                "how": how}
 
 
 def gemm_traffic(n, nm, alg_bytes):
