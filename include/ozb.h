@@ -233,6 +233,13 @@ int ozb_gemm_i8(const int8_t *A, const int8_t *Bt, int32_t *C, int M, int N, int
  * ozb_modulus(first_modulus + z); ldc a multiple of 16 */
 int ozb_gemm_i8_mod(const int8_t *A, const int8_t *Bt, int8_t *C, int M, int N, int K, int Z, long long lda, long long ldb,
                     long long ldc, size_t plane_a, size_t plane_b, size_t plane_c, int first_modulus, void *stream);
+/* The same beside other kernels that need SMs while it runs (the transfer kernels of a broadcast in flight): the
+ * persistent grid leaves `reserve_sms` SMs free. With `busy` (a device word, may be NULL) that is decided on the device:
+ * every CTA pair is launched, and the pairs that would have been left out leave at once if *busy is non-zero when they
+ * start and work otherwise. No counterpart in the reference (it has no multi-GPU path). */
+int ozb_gemm_i8_mod_beside(const int8_t *A, const int8_t *Bt, int8_t *C, int M, int N, int K, int Z, long long lda,
+                           long long ldb, long long ldc, size_t plane_a, size_t plane_b, size_t plane_c, int first_modulus,
+                           int reserve_sms, const int *busy, void *stream);
 /* src/ozaki2.cuh:82-97 (oz::crt) -- from int32 planes of raw products (the reference's layout) */
 int ozb_crt_i32(int moduli, const int32_t *Cl, size_t plane, int M, int N, long long ldr, const int *sa, const int *sb,
                 double *C, long long ldc, void *stream);

@@ -60,6 +60,7 @@ lib.ozb_scale_residues_cols.argtypes = [_i, _p, _i, _i, _ll, _i, _p, _p, _p, _i,
 lib.ozb_scale_residues_cols_static.argtypes = [_i, _p, _i, _i, _ll, _i, _p, _p, _i, _sz, _p]
 lib.ozb_gemm_i8.argtypes = [_p, _p, _p, _i, _i, _i, _i, _ll, _ll, _ll, _sz, _sz, _sz, _p]
 lib.ozb_gemm_i8_mod.argtypes = [_p, _p, _p, _i, _i, _i, _i, _ll, _ll, _ll, _sz, _sz, _sz, _i, _p]
+lib.ozb_gemm_i8_mod_beside.argtypes = [_p, _p, _p, _i, _i, _i, _i, _ll, _ll, _ll, _sz, _sz, _sz, _i, _i, _p, _p]
 lib.ozb_crt_i32.argtypes = [_i, _p, _sz, _i, _i, _ll, _p, _p, _p, _ll, _p]
 lib.ozb_crt_i8.argtypes = [_i, _p, _sz, _i, _i, _ll, _p, _p, _p, _ll, _p]
 lib.ozb_int8_peak.argtypes = [_i, _i, ctypes.POINTER(ctypes.c_float), ctypes.POINTER(ctypes.c_double)]
@@ -84,7 +85,7 @@ SYMBOLS = [
     "ozb_version", "ozb_error", "ozb_device", "ozb_dgemm", "ozb_ddgemm", "ozb_tdgemm", "ozb_release", "ozb_bench",
     "ozb_bits_for", "ozb_modulus", "ozb_plan_create", "ozb_plan_destroy", "ozb_plan_dgemm", "ozb_plan_set_a",
     "ozb_plan_panel", "ozb_plan_b_begin", "ozb_plan_b_rows", "ozb_plan_b_finish", "ozb_plan_multiply", "ozb_cols_absmax", "ozb_plan_b_rows_residues", "ozb_plan_view", "ozb_plan_status", "ozb_plan_profile", "ozb_plan_phase_ms", "ozb_plan_kernel_ms", "ozb_dgemm_ex", "ozb_dgemm_norm", "ozb_scales_norm", "ozb_ddgemm_ex", "ozb_bf16_fp8_gemm",
-    "ozb_scale_residues_rows", "ozb_scale_residues_cols", "ozb_scale_residues_cols_static", "ozb_gemm_i8", "ozb_gemm_i8_mod", "ozb_crt_i32", "ozb_crt_i8",
+    "ozb_scale_residues_rows", "ozb_scale_residues_cols", "ozb_scale_residues_cols_static", "ozb_gemm_i8", "ozb_gemm_i8_mod", "ozb_gemm_i8_mod_beside", "ozb_crt_i32", "ozb_crt_i8",
     "ozb_status", "ozb_int8_peak", "ozb_selftest_wait_expiry", "ozb_bounds_report", "ozb_selftest_bounds",
     "ozb_dgemm_mg", "ozb_mg_release", "ozb_mg_unique_id", "ozb_mg_create", "ozb_mg_destroy", "ozb_mg_dgemm", "ozb_mg_wait", "ozb_mg_info", "ozb_mg_schedule",
 ]

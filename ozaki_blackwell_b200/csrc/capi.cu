@@ -151,7 +151,7 @@ static int plan_make(int M, int N, int K, int nm, int maxbits, ozb_plan **out) {
 // not (measured: 1.8 instead of 3.2 POP/s, the kernel turns HBM-bound); later chunks add to the residues the earlier ones
 // stored. `accumulate` says whether the first chunk already finds residues of an earlier part of K in Cr.
 static cudaError_t gemm_range(ozb_plan *p, const int8_t *Br, int8_t *Cr, int n, cudaStream_t st, int i0, int m, int k0, int klen,
-                              int accumulate, int *launches = nullptr, int reserve_sms = 0) {
+                              int accumulate, int *launches = nullptr, int reserve_sms = 0, const int *yield_flag = nullptr) {
     if (m < 0) m = p->M;   // rows [i0, i0 + m) of A and C
     static const int target = [] { const char *env = getenv("OZ_KCHUNK"); const int v = env && *env ? atoi(env) : 0; return v >= 1024 ? v : 8192; }();
     const int chunks = klen > target + target / 2 ? (klen + target - 1) / target : 1;
@@ -159,7 +159,7 @@ static cudaError_t gemm_range(ozb_plan *p, const int8_t *Br, int8_t *Cr, int n, 
     for (int k = k0, i = 0; k < k0 + klen; k += kc, i++) {
         const int len = k0 + klen - k < kc ? k0 + klen - k : kc;
         cudaError_t e = gemm_i8_planes(p->Ar + (size_t)i0 * p->Kp + k, Br + k, Cr + (size_t)i0 * p->Np, m, n, len, p->nm, p->Kp, p->Kp,
-                                       p->Np, p->planeA, p->planeB, p->planeC, 1, 0, p->status, 0, st, accumulate || i > 0, reserve_sms);
+                                       p->Np, p->planeA, p->planeB, p->planeC, 1, 0, p->status, 0, st, accumulate || i > 0, reserve_sms, yield_flag);
         if (e) return e;
         if (launches) ++*launches;
     }
@@ -169,8 +169,8 @@ static cudaError_t gemm_chunks(ozb_plan *p, const int8_t *Br, int8_t *Cr, int n,
     return gemm_range(p, Br, Cr, n, st, i0, m, 0, p->K, 0);
 }
 cudaError_t ozb_plan_gemm_range(ozb_plan *p, int n, int k0, int klen, int accumulate, cudaStream_t st, int i0, int m, int *launches,
-                                int reserve_sms) {
-    return gemm_range(p, p->Br, p->Cr, n, st, i0, m, k0, klen, accumulate, launches, reserve_sms);
+                                int reserve_sms, const int *yield_flag) {
+    return gemm_range(p, p->Br, p->Cr, n, st, i0, m, k0, klen, accumulate, launches, reserve_sms, yield_flag);
 }
 
 // a plan's workspaces live on the device that was current when it was made: launching from another one would read them
@@ -794,6 +794,18 @@ OZB_API int ozb_gemm_i8_mod(const int8_t *A, const int8_t *Bt, int8_t *C, int M,
     if (!st) return (int)cudaErrorMemoryAllocation;
     return (int)gemm_i8_planes(A, Bt, C, M, N, K, Z, lda, ldb, ldc, plane_a, plane_b, plane_c, 1, first_modulus, st, 0,
                                (cudaStream_t)stream);
+}
+OZB_API int ozb_gemm_i8_mod_beside(const int8_t *A, const int8_t *Bt, int8_t *C, int M, int N, int K, int Z, long long lda,
+                                   long long ldb, long long ldc, size_t plane_a, size_t plane_b, size_t plane_c, int first_modulus,
+                                   int reserve_sms, const int *busy, void *stream) {
+    if (int e = check_args(M, N, K)) return e;
+    if (!A || !Bt || !C || Z <= 0 || lda < K || ldb < K || ldc < round_up(N, 16) || (plane_c & 15) ||
+        (reinterpret_cast<uintptr_t>(C) & 15) || reserve_sms < 0)
+        return OZB_EARG;
+    int *st = status_word();
+    if (!st) return (int)cudaErrorMemoryAllocation;
+    return (int)gemm_i8_planes(A, Bt, C, M, N, K, Z, lda, ldb, ldc, plane_a, plane_b, plane_c, 1, first_modulus, st, 0,
+                               (cudaStream_t)stream, 0, reserve_sms, busy);
 }
 OZB_API int ozb_crt_i32(int moduli, const int32_t *Cl, size_t plane, int M, int N, long long ldr, const int *sa, const int *sb,
                         double *C, long long ldc, void *stream) {

@@ -123,6 +123,8 @@ struct Params {
     size_t plane_c;               // plane pitch of C in elements
     int *status;                  // device word: set to 1 when a wait timed out
     int *counter;                 // two-CTA kernel: next work item, zeroed before the launch
+    const int *yield_flag;        // two-CTA kernel: pairs from `keep_pairs` on leave at once while this word is non-zero (nullptr: nobody leaves)
+    int keep_pairs;               // pairs that always work; the first item of pair i < keep_pairs is item i
 };
 
 struct ModTable { ModConsts v[MAXM]; };
@@ -520,7 +522,12 @@ gemm_i8_tc2(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
             for (uint32_t n = 0; !*abortp; n++) {
                 const int s = n % WORK_SLOTS;
                 if (!mbar_wait(taken_bar(s), ((n / WORK_SLOTS) & 1u) ^ 1u, abortp, 0x70)) break;
-                int w = n == 0 ? pair : npairs + atomicAdd(p.counter, 1);
+                // a pair beyond keep_pairs gives its SMs up when it starts while transfers are outstanding: the kernels that
+                // carry them need SMs, and a persistent pair would hold these until the launch ends
+                int w;
+                if (n == 0 && pair < p.keep_pairs) w = pair;
+                else if (n == 0 && p.yield_flag && *(const volatile int *)p.yield_flag != 0) w = -1;
+                else w = p.keep_pairs + atomicAdd(p.counter, 1);
                 if (w >= total) w = -1;
                 asm volatile("st.shared.b32 [%0], %1;" ::"r"(work_ring + 4u * s), "r"(w) : "memory");
                 asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(map_to_cta(work_ring + 4u * s, 0)), "r"(w) : "memory");
@@ -738,9 +745,11 @@ static int *next_work_counter() {
 // adds the residues already in C before reducing: the caller splits a long K into chunks whose panels stay in L2.
 // `reserve_sms` SMs are left free: a persistent grid never gives an SM back before the launch ends, so a kernel that must
 // start while this one runs (the next transfer of a broadcast in flight) needs SMs that this launch does not take.
+// With `yield_flag` (a device word) the two-CTA kernel decides that on the device instead: every pair is launched, and the
+// pairs that would have been left out leave at once if the word is non-zero when they start, and work otherwise.
 cudaError_t gemm_i8_planes(const int8_t *A, const int8_t *Bt, void *C, int M, int N, int K, int Z, long long lda, long long ldb,
                            long long ldc, size_t pa, size_t pb, size_t pc, int fused, int first_modulus, int *status, int sms,
-                           cudaStream_t st, int accumulate, int reserve_sms) {
+                           cudaStream_t st, int accumulate, int reserve_sms, const int *yield_flag) {
     if (M <= 0 || N <= 0 || K <= 0 || Z <= 0 || (accumulate && !fused)) return cudaErrorInvalidValue;
     if (fused && ((ldc & 15) || first_modulus < 0 || first_modulus + Z > MAXM)) return cudaErrorInvalidValue;
     cudaError_t e = gemm_setup();
@@ -799,7 +808,11 @@ cudaError_t gemm_i8_planes(const int8_t *A, const int8_t *Bt, void *C, int M, in
         const long long pairs_total = (long long)((M + g8::two::BM2 - 1) / g8::two::BM2) * p.tiles_n * Z;
         int limit = mp[fused ? 1 : 0] - (reserve_sms > 0 ? (reserve_sms + 1) / 2 : 0);
         if (limit < 1) limit = 1;
-        const int pairs = (int)(pairs_total < limit ? pairs_total : limit);
+        const int all = mp[fused ? 1 : 0];
+        const int keep = (int)(pairs_total < limit ? pairs_total : limit);
+        const int pairs = yield_flag ? (int)(pairs_total < all ? pairs_total : all) : keep;
+        p.keep_pairs = keep;
+        p.yield_flag = pairs > keep ? yield_flag : nullptr;
         if (!(p.counter = next_work_counter())) return cudaErrorInvalidDevice;
         if ((e = cudaMemsetAsync(p.counter, 0, sizeof(int), st))) return e;
         if (fused) g8::gemm_i8_tc2<true><<<2 * pairs, g8::THREADS, g8::two::SMEM2_BYTES, st>>>(mapA, mapB, p);

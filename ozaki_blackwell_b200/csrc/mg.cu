@@ -92,6 +92,7 @@ constexpr int MG_MAX_PIECES = 64, MG_MAX_BLOCKS = 32;
 struct ozb_mg {
     int world, rank, dev, timeout_ms;
     int reserve_sms;                   // SMs the GEMMs leave to NCCL's kernels while transfers are outstanding (its CTA cap)
+    int *pending;                      // device word: non-zero while pieces of B are still to come (set and cleared on sComm)
     ncclComm_t comm;                   // every transfer that is waited for: as many CTAs as NCCL likes
     ncclComm_t comm_beside;            // transfers that run beside the GEMMs (the stream layout): CTAs capped, SMs reserved for them
     bool broken;                       // the communicator was aborted: every later call answers OZB_ECOMM
@@ -101,6 +102,7 @@ struct ozb_mg {
     double *stageB; size_t stageB_elems;   // this rank's copy of B (receivers; a holder whose B is strided or comes from the host)
     double *dA, *dC; size_t dA_elems, dC_elems;   // host-operand and single-process paths: this rank's rows on its device
     cudaEvent_t mark[96]; char mark_name[96][20]; int marks;   // OZ_MG_TRACE: a timeline of the last product on this rank
+    cudaEvent_t landed[MG_MAX_PIECES]; int landings;           // OZ_MG_TRACE: when each piece of B had arrived (communication stream)
     int last_layout, last_pieces, last_kernels;   // what the last product did (0 whole, 1 stream; transfers of B; kernels of this library), for reports
 };
 
@@ -233,7 +235,8 @@ size_t piece_target(int K, int N) {
 // are launched behind it. A K the single-GPU product runs in one launch (up to 1.5 chunks) stays one launch, after the last
 // piece: only the residues of B are formed piece by piece. A longer K is cut as the single-GPU product cuts it: a first
 // short range of about 2048 (one piece of half the usual size: the GEMMs start early), a second of about 4096, then about
-// 8192 each; arrival (about 240 GB/s with NCCL's capped kernels) stays ahead of the GEMMs from there on.
+// 8192 each; arrival (about 400 GB/s with NCCL's kernels capped to 32 CTAs, measured beside the GEMMs on four B200s) stays
+// ahead of the GEMMs from there on.
 struct Piece { int k0, len, range_k0, range_len; };   // range_len > 0: the GEMMs of [range_k0, range_k0 + range_len) follow this piece
 int stream_schedule(int K, int N, Piece *out) {
     static const int kchunk = [] { const char *env = getenv("OZ_KCHUNK"); const int v = env && *env ? atoi(env) : 0; return v >= 1024 ? v : 8192; }();
@@ -266,16 +269,31 @@ void mg_mark(ozb_mg *g, cudaStream_t st, const char *name, int i = -1) {
     cudaEventRecord(ev, st);
     g->marks++;
 }
+void mg_landed(ozb_mg *g, int i) {
+    static const bool trace = getenv("OZ_MG_TRACE") != nullptr;
+    if (!trace || i >= MG_MAX_PIECES) return;
+    if (!g->landed[i] && cudaEventCreate(&g->landed[i]) != cudaSuccess) return;
+    cudaEventRecord(g->landed[i], g->sComm);
+    g->landings = i + 1;
+}
 void mg_print_marks(ozb_mg *g) {
     if (g->marks < 2) return;
-    fprintf(stderr, "ozb mg rank %d timeline (ms):", g->rank);
-    for (int i = 1; i < g->marks; i++) {
+    char line[4096];   // one write per rank: the ranks of a job share the terminal
+    int at = snprintf(line, sizeof line, "ozb mg rank %d timeline (ms):", g->rank);
+    for (int i = 1; i < g->marks && at < (int)sizeof line - 64; i++) {
         float t = 0;
-        if (cudaEventElapsedTime(&t, g->mark[i - 1], g->mark[i]) == cudaSuccess) fprintf(stderr, " %s %.2f", g->mark_name[i], t);
+        if (cudaEventElapsedTime(&t, g->mark[i - 1], g->mark[i]) == cudaSuccess) at += snprintf(line + at, sizeof line - at, " %s %.2f", g->mark_name[i], t);
     }
     float all = 0;
     cudaEventElapsedTime(&all, g->mark[0], g->mark[g->marks - 1]);
-    fprintf(stderr, " | total %.2f\n", all);
+    at += snprintf(line + at, sizeof line - at, " | total %.2f", all);
+    if (g->landings) at += snprintf(line + at, sizeof line - at, " | pieces landed at");
+    for (int i = 0; i < g->landings && at < (int)sizeof line - 32; i++) {
+        float t = 0;
+        if (cudaEventElapsedTime(&t, g->mark[0], g->landed[i]) == cudaSuccess) at += snprintf(line + at, sizeof line - at, " %.1f", t);
+    }
+    snprintf(line + at, sizeof line - at, "\n");
+    fputs(line, stderr);
 }
 
 // C_local = A_local B on device operands; B is read on `root` only. Asynchronous on `st` (and the handle's own
@@ -295,7 +313,7 @@ int mg_dgemm_dev(ozb_mg *g, int m, int N, int K, const double *A, long long lda,
     // order: after the caller's writes of A and B (stream st), and after the previous product's reads of the staging copy
     if (src && !in_place) e = cudaMemcpy2DAsync(g->stageB, (size_t)N * 8, B, (size_t)ldb * 8, (size_t)N * 8, K, cudaMemcpyDeviceToDevice, st);
     if (!e) e = cudaMemsetAsync(p->colmax, 0, (size_t)N * 8, st);
-    g->marks = 0;
+    g->marks = 0; g->landings = 0;
     mg_mark(g, st, "start");
     int kernels = 2;   // the residues of A and the reconstruction; counted below: maxima, residues of B, GEMM launches
     if (!e && layout == LAYOUT_STREAM && src) { e = cols_absmax_accumulate(whole, K, N, N, p->colmax, st); kernels++; }
@@ -327,11 +345,17 @@ int mg_dgemm_dev(ozb_mg *g, int m, int N, int K, const double *A, long long lda,
     } else {
         Piece sched[MG_MAX_PIECES];
         pieces = stream_schedule(K, N, sched);
+        // OZ_MG_YIELD=0: the GEMMs of every range but the last leave NCCL's SMs free whatever the transfers do
+        static const bool yield = [] { const char *env = getenv("OZ_MG_YIELD"); return !(env && *env == '0'); }();
+        const bool beside = g->world > 1 && g->reserve_sms > 0;
+        if (beside) if ((e = cudaMemsetAsync(g->pending, 1, sizeof(int), g->sComm))) return (int)e;
         if (int c = mg_bcast(g, p->colmax, (size_t)N * 8, root, true)) return c;   // the column maxima, ahead of B on the same stream
         for (int i = 0, ranges = 0; i < pieces && !e; i++) {
             const Piece &pc = sched[i];
             if (int c = mg_bcast(g, whole + (size_t)pc.k0 * N, (size_t)pc.len * N * 8, root, true)) return c;
+            if (beside && i == pieces - 1) if ((e = cudaMemsetAsync(g->pending, 0, sizeof(int), g->sComm))) break;
             if ((e = cudaEventRecord(g->evPiece[i], g->sComm))) break;
+            mg_landed(g, i);
             if (!src) e = cudaStreamWaitEvent(st, g->evPiece[i], 0);
             mg_mark(g, st, "wait", i);
             if (!e) e = cols_residues_from_max(nm, whole + (size_t)pc.k0 * N, pc.len, N, N, p->bits, p->colmax, p->sb, p->Br + pc.k0, p->Kp, p->planeB, st);
@@ -340,9 +364,11 @@ int mg_dgemm_dev(ozb_mg *g, int m, int N, int K, const double *A, long long lda,
             if (!e && pc.range_len) {
                 // A persistent GEMM gives no SM back before it ends, and the transfer of the next piece is a kernel of its
                 // own that starts when the one before it has finished: while pieces are still to come, the GEMMs leave
-                // NCCL's SMs free (the last range starts after the last piece has landed and takes them all).
-                const int reserve = g->world > 1 && i < pieces - 1 ? g->reserve_sms : 0;
-                e = ozb_plan_gemm_range(p, N, pc.range_k0, pc.range_len, ranges++ > 0, st, 0, -1, &kernels, reserve);
+                // NCCL's SMs free. Whether pieces are still to come is read on the device when a CTA pair starts (the word
+                // `pending`, cleared on the communication stream behind the last piece): the host queues the launches long
+                // before they run and cannot know. The last range starts after the last piece and takes every SM.
+                const int reserve = beside && (yield || i < pieces - 1) ? g->reserve_sms : 0;
+                e = ozb_plan_gemm_range(p, N, pc.range_k0, pc.range_len, ranges++ > 0, st, 0, -1, &kernels, reserve, yield ? g->pending : nullptr);
                 mg_mark(g, st, "gemm", ranges - 1);
             }
         }
@@ -469,6 +495,8 @@ OZB_API int ozb_mg_create(int world, int rank, const void *id, int timeout_ms, o
     for (auto &ev : g->evPiece) if (!e) e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
     for (auto &ev : g->evIn) if (!e) e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
     for (auto &ev : g->evRun) if (!e) e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+    if (!e) e = cudaMalloc(&g->pending, sizeof(int));
+    if (!e) e = cudaMemset(g->pending, 0, sizeof(int));
     int rc = (int)e;
     if (!rc && world > 1) {
         ncclUniqueId u;
@@ -482,7 +510,10 @@ OZB_API int ozb_mg_create(int world, int rank, const void *id, int timeout_ms, o
             rc = mg_settle(g, r);
         }
         // A second communicator over the same ranks for the transfers that run beside the GEMMs: its kernels are capped to a
-        // few CTAs (OZ_MG_MAX_CTAS, default 16) and the GEMMs leave as many SMs free (OZ_MG_RESERVE_SMS). Transfers that are
+        // few CTAs (OZ_MG_MAX_CTAS, default 32) and the GEMMs leave as many SMs free (OZ_MG_RESERVE_SMS) while pieces are still
+        // to come. Measured beside the GEMMs on four B200s, 1 GiB pieces: 16 CTAs deliver 114 GB/s (the 8 GiB of B at
+        // n = 32768 take 62 ms -- longer than an eighth of that product), 24 CTAs 330 GB/s, 32 CTAs 405 GB/s; what the GEMMs
+        // lose is SMs x time, about the same 4 - 5 ms from 24 CTAs up. Transfers that are
         // waited for keep the first communicator and all the CTAs NCCL wants: capped, a 512 MiB broadcast between four
         // B200s took 0.9 ms longer.
         g->comm_beside = g->comm;
@@ -507,7 +538,7 @@ OZB_API int ozb_mg_create(int world, int rank, const void *id, int timeout_ms, o
                 ncclConfig_t cap = NCCL_CONFIG_INITIALIZER;
                 cap.blocking = 0;
                 const char *env = getenv("OZ_MG_MAX_CTAS");
-                cap.maxCTAs = env && atoi(env) > 0 ? atoi(env) : 16;
+                cap.maxCTAs = env && atoi(env) > 0 ? atoi(env) : 32;
                 ncclComm_t second = nullptr;
                 ncclResult_t r = nccl().CommInitRankConfig(&second, world, u2, rank, &cap);
                 if (second) g->comm_beside = second;          // from here on an abort takes it along
@@ -545,13 +576,14 @@ OZB_API void ozb_mg_destroy(ozb_mg *g) {
         abort_comms(g->comm, g->comm_beside != g->comm ? g->comm_beside : nullptr, g->timeout_ms);
     }
     if (g->plan) ozb_plan_free_internal(g->plan);
-    cudaFree(g->stageB); cudaFree(g->dA); cudaFree(g->dC);
+    cudaFree(g->stageB); cudaFree(g->dA); cudaFree(g->dC); cudaFree(g->pending);
     for (cudaStream_t s : {g->sComm, g->sIn, g->sRun, g->sOut}) if (s) cudaStreamDestroy(s);
     for (cudaEvent_t ev : {g->evStart, g->evDone}) if (ev) cudaEventDestroy(ev);
     for (auto ev : g->evPiece) if (ev) cudaEventDestroy(ev);
     for (auto ev : g->evIn) if (ev) cudaEventDestroy(ev);
     for (auto ev : g->evRun) if (ev) cudaEventDestroy(ev);
     for (auto ev : g->mark) if (ev) cudaEventDestroy(ev);
+    for (auto ev : g->landed) if (ev) cudaEventDestroy(ev);
     delete g;
     if (cur >= 0 && cur != dev) cudaSetDevice(cur);
 }

@@ -20,7 +20,7 @@ cudaError_t norm_scale_residues_cols(int nm, const double *X, int rows, int cols
                                      size_t plane, cudaStream_t st);
 cudaError_t gemm_i8_planes(const int8_t *A, const int8_t *Bt, void *C, int M, int N, int K, int Z, long long lda, long long ldb,
                            long long ldc, size_t pa, size_t pb, size_t pc, int fused, int first_modulus, int *status, int sms,
-                           cudaStream_t st, int accumulate = 0, int reserve_sms = 0);
+                           cudaStream_t st, int accumulate = 0, int reserve_sms = 0, const int *yield_flag = nullptr);
 cudaError_t int8_peak_probe(int iters, int pair, float *ms, double *tops, int *status, cudaStream_t st);
 cudaError_t wait_expiry_selftest(unsigned budget_ms, int *status, cudaStream_t st);
 cudaError_t crt_from_i8(int nm, const int8_t *Cr, size_t plane, int M, int N, long long ldr, const int *sa, const int *sb,

@@ -40,5 +40,6 @@ void ozb_plan_free_internal(ozb_plan *p);
 // first n columns; accumulate != 0 adds to the residues already in Cr (an earlier part of K)
 cudaError_t ozb_plan_gemm_range(ozb_plan *p, int n, int k0, int klen, int accumulate, cudaStream_t st, int i0 = 0, int m = -1,
                                 int *launches = nullptr,    // *launches is incremented per GEMM kernel launched
-                                int reserve_sms = 0);       // SMs the launches leave free for kernels that must start beside them
+                                int reserve_sms = 0,        // SMs the launches leave free for kernels that must start beside them
+                                const int *yield_flag = nullptr);   // device word: leave them free only while it is non-zero
 int ozb_read_status_words(int *dev_words);

@@ -75,6 +75,36 @@ def test_gemm_i8_fused_mod_matches_balanced_residue():
         assert np.array_equal(got[z], want), (z, m, g.describe_mismatch(got[z], want))
 
 
+@pytest.mark.parametrize("busy", [None, 0, 1])
+def test_gemm_i8_beside_other_kernels_same_residues(busy):
+    """The persistent grid that leaves SMs to other kernels: with the decision on the host (busy None), and on the device
+    with the word clear (every CTA pair works) or set (the pairs beyond the kept ones leave when they start). More tiles
+    than resident pairs, so the pairs that stay take over what the leavers would have done."""
+    import torch
+    g = _gu()
+    Z, M, N, K = 6, 1100, 2300, 384
+    rng = np.random.default_rng(41)
+    A = rng.integers(-128, 128, size=(Z, M, K), dtype=np.int8)
+    Bt = rng.integers(-128, 128, size=(Z, N, K), dtype=np.int8)
+    Kp, Np = g.round_up(K, 16), g.round_up(N, 16)
+    Ad = torch.zeros((Z, M, Kp), dtype=torch.int8, device="cuda")
+    Bd = torch.zeros((Z, N, Kp), dtype=torch.int8, device="cuda")
+    Ad[:, :, :K] = g.dev(A)
+    Bd[:, :, :K] = g.dev(Bt)
+    word = None if busy is None else torch.tensor([busy], dtype=torch.int32, device="cuda")
+    for reserve in (16, 64, 1000):      # 1000: more than the device has -- one pair is always kept
+        C = torch.full((Z, M, Np), 99, dtype=torch.int8, device="cuda")
+        g.check(g.lib.ozb_gemm_i8_mod_beside(g.ptr(Ad), g.ptr(Bd), g.ptr(C), M, N, K, Z, Kp, Kp, Np, M * Kp, N * Kp, M * Np, 3,
+                                             reserve, None if word is None else g.ptr(word), None))
+        g.check(g.lib.ozb_status())
+        got = C.cpu().numpy()[:, :, :N]
+        for z in range(Z):
+            m = o.modulus(3 + z)
+            r = np.mod(o.gemm_i8(A[z], Bt[z]).astype(np.int64), m)
+            want = np.where(r >= (m + 1) // 2, r - m, r).astype(np.int8)
+            assert np.array_equal(got[z], want), (busy, reserve, z, g.describe_mismatch(got[z], want))
+
+
 def test_gemm_mutant_is_detected():
     """The comparison itself must notice a single flipped byte (the reference's mutation check, bench/oz_strassen.cu:299-308)."""
     g = _gu()
