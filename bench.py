@@ -360,6 +360,8 @@ class Bench:
         n, nm = args.n, args.moduli
         N = K = n
         M = n // world if args.strong else n            # rows of A and C per rank (weak: n each; --strong: n in total)
+        if args.rows > 0:
+            M = args.rows                               # a chosen share per rank: what a rank of a larger job would hold
         A = synthetic(M, K, 1000 + rank, dev)
         B = synthetic(K, N, 7, dev) if rank == 0 else None
         C = torch.empty((M, N), dtype=torch.float64, device=dev)
@@ -489,6 +491,9 @@ class Bench:
                 raise RuntimeError("GPU result differs from the CPU checker on the sampled block")
 
         config = workload_config(n, nm, world)
+        if M != n:
+            config["workload"] = config["workload"].replace(f"{world} row block(s) of {n} rows", f"{world} row block(s) of {M} rows")
+            config["M_total"] = M * world
         dist_info = None if world == 1 else {"broadcast_layout": op.layout, "pieces": len(op.ranges)}
         if plan is not None:
             lib.ozb_plan_destroy(plan)
@@ -650,6 +655,7 @@ def main():
     ap.add_argument("--panels", type=int, default=None, help="pieces B is broadcast in (N > 1; default: by the size of B)")
     ap.add_argument("--layout", choices=("auto", "rows", "panels"), default="auto", help="broadcast B in row chunks or in column panels (N > 1)")
     ap.add_argument("--strong", action="store_true", help="make the headline run itself a strong split of the n x n x n product")
+    ap.add_argument("--rows", type=int, default=0, help="rows of A and C per rank, whatever N is (e.g. 4096 with --size 32768: a rank's share at eight GPUs)")
     ap.add_argument("--strong-size", type=int, default=32768, help="n of the strong-scaling case reported beside the headline (0: skip)")
     ap.add_argument("--strong-steps", type=int, default=3)
     ap.add_argument("--e2e-steps", type=int, default=10)

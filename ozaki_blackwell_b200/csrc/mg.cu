@@ -510,10 +510,12 @@ OZB_API int ozb_mg_create(int world, int rank, const void *id, int timeout_ms, o
             rc = mg_settle(g, r);
         }
         // A second communicator over the same ranks for the transfers that run beside the GEMMs: its kernels are capped to a
-        // few CTAs (OZ_MG_MAX_CTAS, default 32) and the GEMMs leave as many SMs free (OZ_MG_RESERVE_SMS) while pieces are still
-        // to come. Measured beside the GEMMs on four B200s, 1 GiB pieces: 16 CTAs deliver 114 GB/s (the 8 GiB of B at
-        // n = 32768 take 62 ms -- longer than an eighth of that product), 24 CTAs 330 GB/s, 32 CTAs 405 GB/s; what the GEMMs
-        // lose is SMs x time, about the same 4 - 5 ms from 24 CTAs up. Transfers that are
+        // few CTAs (OZ_MG_MAX_CTAS; default 32, 16 between two ranks) and the GEMMs leave as many SMs free (OZ_MG_RESERVE_SMS)
+        // while pieces are still to come. Measured beside the GEMMs, 1 GiB pieces: among four B200s (every rank receives and
+        // forwards) 16 CTAs deliver 114 GB/s (the 8 GiB of B at n = 32768 take 62 ms -- longer than an eighth of that
+        // product), 24 CTAs 330 GB/s, 32 CTAs 405 GB/s; between two B200s 16 CTAs deliver 350 GB/s and 32 CTAs 580 GB/s, and a
+        // 4096-row share of that product takes 60.7 ms with 16, 61.9 with 32, 63.3 with 48 (58.1 with no transfer at all).
+        // Transfers that are
         // waited for keep the first communicator and all the CTAs NCCL wants: capped, a 512 MiB broadcast between four
         // B200s took 0.9 ms longer.
         g->comm_beside = g->comm;
@@ -538,7 +540,7 @@ OZB_API int ozb_mg_create(int world, int rank, const void *id, int timeout_ms, o
                 ncclConfig_t cap = NCCL_CONFIG_INITIALIZER;
                 cap.blocking = 0;
                 const char *env = getenv("OZ_MG_MAX_CTAS");
-                cap.maxCTAs = env && atoi(env) > 0 ? atoi(env) : 32;
+                cap.maxCTAs = env && atoi(env) > 0 ? atoi(env) : world <= 2 ? 16 : 32;
                 ncclComm_t second = nullptr;
                 ncclResult_t r = nccl().CommInitRankConfig(&second, world, u2, rank, &cap);
                 if (second) g->comm_beside = second;          // from here on an abort takes it along
