@@ -367,7 +367,7 @@ int mg_dgemm_dev(ozb_mg *g, int m, int N, int K, const double *A, long long lda,
                 // NCCL's SMs free. Whether pieces are still to come is read on the device when a CTA pair starts (the word
                 // `pending`, cleared on the communication stream behind the last piece): the host queues the launches long
                 // before they run and cannot know. The last range starts after the last piece and takes every SM.
-                const int reserve = beside && (yield || i < pieces - 1) ? g->reserve_sms : 0;
+                const int reserve = beside && i < pieces - 1 ? g->reserve_sms : 0;
                 e = ozb_plan_gemm_range(p, N, pc.range_k0, pc.range_len, ranges++ > 0, st, 0, -1, &kernels, reserve, yield ? g->pending : nullptr);
                 mg_mark(g, st, "gemm", ranges - 1);
             }
