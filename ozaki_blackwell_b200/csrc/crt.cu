@@ -37,8 +37,14 @@ __device__ __forceinline__ void garner_digits(uint32_t (&X)[E][(NM + 3) / 4]) {
         constexpr int lift = lift_of(l, GARNER_BOUND) - half_of(l);   // a multiple of m_l; the balancing shift is folded into balanced_magic
         static_assert(lift > GARNER_BOUND && magic_ok(l, (uint64_t)lift + half_of(l) + GARNER_BOUND), "multiply-high reduction out of range");
         int acc[E];
+#ifndef OZ_INT_REDUCE
+        static_assert(GARNER_BOUND < (1 << 22), "the dot product must fit the float's mantissa");
+#pragma unroll
+        for (int e = 0; e < E; e++) acc[e] = FLOAT_BIAS;
+#else
 #pragma unroll
         for (int e = 0; e < E; e++) acc[e] = lift;
+#endif
         // digits x_0..x_{l-1} have already replaced the residues in the low bytes; byte l still holds r_l
         static_for<0, l / 4 + 1>([&](auto G) {
             constexpr int g = decltype(G)::value;
@@ -50,7 +56,11 @@ __device__ __forceinline__ void garner_digits(uint32_t (&X)[E][(NM + 3) / 4]) {
         constexpr uint32_t sel = l % 4 == 0 ? 0x3214u : l % 4 == 1 ? 0x3240u : l % 4 == 2 ? 0x3410u : 0x4210u;
 #pragma unroll
         for (int e = 0; e < E; e++) {
+#ifndef OZ_INT_REDUCE
+            const uint32_t xl = balanced_float<l>(acc[e]);                               // balanced digit, low byte
+#else
             const uint32_t xl = balanced_magic<l>((uint32_t)acc[e]);                     // balanced digit, low byte
+#endif
             X[e][l / 4] = __byte_perm(X[e][l / 4], xl, sel);                             // byte l%4 <- xl
         }
     });

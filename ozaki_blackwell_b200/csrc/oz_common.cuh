@@ -59,6 +59,22 @@ __device__ __forceinline__ uint32_t balanced_magic(uint32_t a) {
     return u - __umulhi(u, magic_of(L)) * (uint32_t)modulus(L) - (uint32_t)half_of(L);
 #endif
 }
+// The same balanced residue on the FP32 pipes. `biased` is the signed sum S on top of the bit pattern of 1.5 * 2^23
+// (FLOAT_BIAS: seed the dp4a chain with it and the sum lands in the mantissa, so the word read as a float IS 1.5 * 2^23 + S).
+// q = rint(S / m) by the add-and-subtract of 1.5 * 2^23, then 1.5 * 2^23 + S - q m in one fused multiply-add; the low
+// byte of that float's bit pattern is the int8 residue. Exact for odd m and |S| < 2^22: S / m computed as S * fl(1/m) is
+// off by less than |S| 2^-24 / m, and S / m is never closer than 1/(2m) to a half-integer; every other step is exact integer
+// arithmetic below 2^24. Four FP32 instructions, which run on either FMA pipe; the multiply-high form keeps two of its four on
+// the one pipe that also runs dp4a.
+constexpr int FLOAT_BIAS = 0x4B400000;   // 1.5 * 2^23 = 12582912.0f
+template <int L>
+__device__ __forceinline__ uint32_t balanced_float(int biased) {
+    static_assert(modulus(L) % 2 == 1, "an even modulus has ties");
+    constexpr float C = 12582912.0f, inv = 1.0f / (float)modulus(L), m = (float)modulus(L);
+    const float A = __int_as_float(biased);
+    const float q = __fadd_rn(__fmaf_rn(__fadd_rn(A, -C), inv, C), -C);
+    return (uint32_t)__float_as_int(__fmaf_rn(q, -m, A));
+}
 // 2^s as a double for -1022 <= s <= 1023
 __device__ __forceinline__ double pow2_normal(int s) { return __hiloint2double((s + 1023) << 20, 0); }
 // llrint(ldexp(x, s)) as the reference computes it (src/ozaki2.cuh:76). For s in the normal exponent range the scaling

@@ -40,8 +40,15 @@ __device__ __forceinline__ void residues_of_4(const long long (&v)[4], Put &&put
         constexpr int init = lift_of(l, BYTES_BOUND) - half_of(l) - pow2_mod(62, m);
         static_assert(init > BYTES_BOUND && magic_ok(l, (uint64_t)init + half_of(l) + BYTES_BOUND), "multiply-high reduction out of range");
         uint32_t x[4];
+#ifndef OZ_INT_REDUCE
+        constexpr int seed = FLOAT_BIAS - pow2_mod(62, m);
+        static_assert(BYTES_BOUND + 256 < (1 << 22), "the byte sum must fit the float's mantissa");
+#pragma unroll
+        for (int e = 0; e < 4; e++) x[e] = balanced_float<l>(dp4a_us(hi[e], whi, dp4a_us(lo[e], wlo, seed)));
+#else
 #pragma unroll
         for (int e = 0; e < 4; e++) x[e] = balanced_magic<l>((uint32_t)dp4a_us(hi[e], whi, dp4a_us(lo[e], wlo, init)));
+#endif
         put(L, pack_low_bytes(x[0], x[1], x[2], x[3]));
     });
 }
