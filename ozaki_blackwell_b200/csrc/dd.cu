@@ -63,6 +63,13 @@ __device__ __forceinline__ void residues_of_4_dd(const long long (&u)[4], const 
         constexpr int init = lift_of(l, DD_BYTES_BOUND) - off;
         static_assert(init > DD_BYTES_BOUND && magic_ok(l, (uint64_t)init + DD_BYTES_BOUND), "multiply-high reduction out of range");
         uint32_t x[4];
+#ifndef OZ_INT_REDUCE   // the reduction on the FP32 pipes (balanced_float): the sum sits on the bit pattern of 1.5 * 2^23
+        constexpr int seed = FLOAT_BIAS - off;
+        static_assert(DD_BYTES_BOUND + 256 < (1 << 22), "the byte sum must fit the float's mantissa");
+#pragma unroll
+        for (int e = 0; e < 4; e++)
+            x[e] = balanced_float<l>(dp4a_us(uh[e], wuh, dp4a_us(ul[e], wul, dp4a_us(th[e], wth, dp4a_us(tl[e], wtl, seed)))));
+#else
 #pragma unroll
         for (int e = 0; e < 4; e++) {
             int acc = dp4a_us(tl[e], wtl, init);
@@ -71,6 +78,7 @@ __device__ __forceinline__ void residues_of_4_dd(const long long (&u)[4], const 
             acc = dp4a_us(uh[e], wuh, acc);
             x[e] = mod_magic<l>((uint32_t)acc) - (uint32_t)half_of(l);
         }
+#endif
         put(L, pack_low_bytes(x[0], x[1], x[2], x[3]));
     });
 }

@@ -137,11 +137,18 @@ __device__ __forceinline__ void residues_of_4_n(const long long (&v)[4], int nm,
             constexpr int init = lift_of(l, BYTES_BOUND) - pow2_mod(62, m);
             static_assert(init > BYTES_BOUND && magic_ok(l, (uint64_t)init + BYTES_BOUND), "multiply-high reduction out of range");
             uint32_t x[4];
+#ifndef OZ_INT_REDUCE   // the reduction on the FP32 pipes (balanced_float)
+            constexpr int seed = FLOAT_BIAS - pow2_mod(62, m);
+            static_assert(BYTES_BOUND + 256 < (1 << 22), "the byte sum must fit the float's mantissa");
+#pragma unroll
+            for (int e = 0; e < 4; e++) x[e] = balanced_float<l>(dp4a_us(hi[e], whi, dp4a_us(lo[e], wlo, seed)));
+#else
 #pragma unroll
             for (int e = 0; e < 4; e++) {
                 const uint32_t u = (uint32_t)dp4a_us(hi[e], whi, dp4a_us(lo[e], wlo, init));
                 x[e] = mod_magic<l>(u) - (uint32_t)half_of(l);
             }
+#endif
             put(l, pack_low_bytes(x[0], x[1], x[2], x[3]));
         }
     });
