@@ -4,10 +4,14 @@
 //   1. residues of a 64-bit integer from its bytes          (scale_residue.cu: residues_of_4)
 //   2. balanced residue of an int32 product by 16-bit split  (gemm_i8_sm100.cu: fused epilogue)
 //   3. Garner digits with one reduction per digit            (crt.cu: garner_horner)
+//   6. the same reductions done in FP32 (oz_common.cuh: balanced_float), which is what the kernels run: every sum in
+//      (-2^22, 2^22) for every odd modulus of the table, and the byte-sum / Garner / double-double forms built on it
 // Each is compared with the reference's definition: bal(x, m) and the step-by-step Garner recurrence
 // (src/ozaki2.cuh:38-42, 86-92 of the reference).
+#include <cmath>
 #include <cstdint>
 #include <cstdio>
+#include <cstring>
 #include <random>
 #include "oz_tables.cuh"
 using namespace ozk;
@@ -29,6 +33,25 @@ template <int L> static uint32_t balanced_magic(uint32_t a) {
     return plain == folded ? plain : 0x7fffffffu;   // both forms must agree; a disagreement shows up as a wrong residue
 }
 static int bal(long long x, int m) { return bal_c(x, m); }
+// oz_common.cuh: balanced_float<L> -- the sum rides on the bit pattern of 1.5 * 2^23; IEEE single arithmetic, fused multiply-adds
+constexpr int FLOAT_BIAS = 0x4B400000;
+static float as_float(int32_t b) { float f; memcpy(&f, &b, 4); return f; }
+static int32_t as_int(float f) { int32_t b; memcpy(&b, &f, 4); return b; }
+template <int L> static uint32_t balanced_float(int biased) {
+    const float C = 12582912.0f, inv = 1.0f / (float)modulus(L), m = (float)modulus(L);
+    const volatile float A = as_float(biased);            // volatile: every step is rounded to single, nothing is re-associated
+    const volatile float f = A - C;
+    const volatile float t = std::fmaf(f, inv, C);
+    const volatile float q = t - C;
+    const volatile float x = std::fmaf(q, -m, A);
+    return (uint32_t)as_int(x);
+}
+template <int L> static long check_float_reduction() {
+    if (modulus(L) % 2 == 0) return 0;                    // 256 is never reduced this way
+    long bad = 0;
+    for (int S = -(1 << 22) + 1; S < (1 << 22); S++) bad += (int)(int8_t)(balanced_float<L>(FLOAT_BIAS + S) & 255) != bal(S, modulus(L));
+    return bad;
+}
 
 template <int L> struct PerMod {
     static int residue_from_bytes(long long v) {
@@ -40,7 +63,10 @@ template <int L> struct PerMod {
         static_assert(init > BYTES_BOUND && magic_ok(l, (uint64_t)init + half_of(l) + BYTES_BOUND), "range");
         const uint64_t w = (uint64_t)v + (1ull << 62);
         const uint32_t u = (uint32_t)dp4a((uint32_t)(w >> 32), whi, dp4a((uint32_t)w, wlo, init, false), false);
-        return (int)(int8_t)(balanced_magic<l>(u) & 255);
+        const int viaint = (int)(int8_t)(balanced_magic<l>(u) & 255);
+        const int seed = FLOAT_BIAS - pow2_mod(62, m);     // scale_residue.cu, exact_f8.cu: the chain seeded for the FP32 form
+        const int viafloat = (int)(int8_t)(balanced_float<l>(dp4a((uint32_t)(w >> 32), whi, dp4a((uint32_t)w, wlo, seed, false), false)) & 255);
+        return viaint == viafloat ? viaint : 0x7fff;
     }
     static int residue_of_product(int32_t x) {
         constexpr ModConsts mc = mod_consts(L);
@@ -62,7 +88,14 @@ template <int NM> static void garner_fast(const int *r, int *x) {   // r: balanc
             for (int q = 0; q < 4; q++) { const int idx = 4 * g + q; c[q] = idx < l ? garner_q(idx, l) : (idx == l ? garner_p(l) : 0); }
             acc = dp4a(X[g], pack4(c[0], c[1], c[2], c[3]), acc, true);
         }
-        const int xl = (int)balanced_magic<l>((uint32_t)acc);
+        int accf = FLOAT_BIAS;                              // crt.cu: the same dot product seeded for the FP32 form
+        for (int g = 0; g <= l / 4; g++) {
+            int c[4];
+            for (int q = 0; q < 4; q++) { const int idx = 4 * g + q; c[q] = idx < l ? garner_q(idx, l) : (idx == l ? garner_p(l) : 0); }
+            accf = dp4a(X[g], pack4(c[0], c[1], c[2], c[3]), accf, true);
+        }
+        const int xi = (int)(int8_t)(balanced_magic<l>((uint32_t)acc) & 255), xf = (int)(int8_t)(balanced_float<l>(accf) & 255);
+        const int xl = xi == xf ? xi : 0x7fff;
         (void)m;
         X[l / 4] = (X[l / 4] & ~(255u << (8 * (l % 4)))) | ((uint32_t)(xl & 255) << (8 * (l % 4)));
         x[l] = xl;
@@ -133,7 +166,14 @@ template <int L> static int dd_residue(long long u, long long t) {
     acc = dp4a((uint32_t)a, pack4(wu[0], wu[1], wu[2], wu[3]), acc, false);
     acc = dp4a((uint32_t)(a >> 32), pack4(wu[4], wu[5], wu[6], wu[7]), acc, false);
     const uint32_t uu = (uint32_t)acc;
-    return (int)(int8_t)((uu - umulhi(uu, magic_of(l)) * (uint32_t)m - (uint32_t)half_of(l)) & 255);
+    const int viaint = (int)(int8_t)((uu - umulhi(uu, magic_of(l)) * (uint32_t)m - (uint32_t)half_of(l)) & 255);
+    int accf = FLOAT_BIAS - off;                           // dd.cu: the chain seeded for the FP32 form
+    accf = dp4a((uint32_t)b, pack4(wt[0], wt[1], wt[2], wt[3]), accf, false);
+    accf = dp4a((uint32_t)(b >> 32), pack4(wt[4], wt[5], wt[6], wt[7]), accf, false);
+    accf = dp4a((uint32_t)a, pack4(wu[0], wu[1], wu[2], wu[3]), accf, false);
+    accf = dp4a((uint32_t)(a >> 32), pack4(wu[4], wu[5], wu[6], wu[7]), accf, false);
+    const int viafloat = (int)(int8_t)(balanced_float<l>(accf) & 255);
+    return viaint == viafloat ? viaint : 0x7fff;
 }
 template <int L> static long check_dd_mod(std::mt19937_64 &g) {
     long bad = 0;
@@ -176,6 +216,7 @@ int main() {
     bad += check_dd_crt<24>(g) + check_dd_crt<28>(g) + check_dd_crt<32>(g);
     static_for<0, MAXM>([&](auto L) { bad += check_mod<decltype(L)::value>(g); });
     static_for<8, 17>([&](auto N) { bad += check_garner<decltype(N)::value>(g); });
+    static_for<1, MAXM>([&](auto L) { bad += check_float_reduction<decltype(L)::value>(); });
     printf("%ld wrong\n", bad);
     return bad != 0;
 }
