@@ -18,10 +18,16 @@
 //           as the pieces of that range are there, adding to the residues of the ranges before it (the same cut of a long
 //           K the single-GPU product makes to keep its panels in L2). The reconstruction runs once at the end.
 //
+//           The pieces travel over a second communicator whose kernels are capped to a few CTAs, and the GEMMs -- persistent
+//           grids that give no SM back before they end -- leave that many SMs alone while pieces are still to come: every
+//           CTA pair is launched, and the pairs beyond the kept ones read a device word when they start (set before the
+//           first piece, cleared behind the last, both on the communication stream) and leave at once if it is set.
+//
 // NCCL is loaded at run time (dlopen of libnccl.so.2: the library itself links against nothing but the driver), the
-// communicator is non-blocking, and every host-side wait is bounded: when a call does not settle or a product does not
-// finish within the handle's time budget -- a peer that never joined -- the communicator is aborted (ncclCommAbort), the
-// handle is marked broken and the call returns OZB_ECOMM; the CUDA context stays usable.
+// communicators are non-blocking, and every host-side wait is bounded: when a call does not settle or a product does not
+// finish within the handle's time budget -- a peer that never joined -- the communicators are aborted (ncclCommAbort, each
+// in a thread of its own, bounded too), the handle is marked broken and the call returns OZB_ECOMM; the CUDA context
+// stays usable.
 #include <nccl.h>
 #include <dlfcn.h>
 #include <atomic>
