@@ -52,6 +52,7 @@ def test_multi_gpu_entry_points_check_their_arguments_first():
     assert lib.ozb_mg_create(2, 0, one, -1, ctypes.byref(h)) == 10001
     assert lib.ozb_mg_dgemm(None, 4, 4, 4, one, 4, one, 4, one, 4, 16, 0, 0, None) == 10001
     assert lib.ozb_mg_wait(None) == 10001 and lib.ozb_mg_info(None, None, None, None) == 10001
+    assert lib.ozb_gemm_i8_mod_beside(one, one, one, 0, 4, 4, 1, 16, 16, 16, 64, 64, 64, 0, 16, None, None) == 10001
     lib.ozb_mg_destroy(None)                                             # tolerated
     assert b"communicator" in lib.ozb_error(10007) and b"NCCL" in lib.ozb_error(10008)
     ident = ctypes.create_string_buffer(128)
