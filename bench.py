@@ -20,6 +20,8 @@ step (weak scaling: M = n * N in total). Rank 0 prints one JSON line.
                bit-compares the GPU result with it
   strong_n32768  BASELINE's large configuration: one n = 32768 product split by row blocks over the N ranks
   ranks_bit_identical  (N > 1) every rank's band of C against the CPU restatement
+--rows R gives every rank R rows of A and C whatever N is (with --strong --size 32768 --rows 4096: the share a rank of
+eight holds, run on fewer GPUs); e2e.ms_last_step_per_rank shows which rank the host link holds up.
 --impl reference times that CPU restatement alone (the reference has no CPU implementation of the Ozaki pipeline of its
 own: its device code is restated in oracle/ozaki2_oracle.c), rank 0 only, on a block sample of the product per step.
 """
