@@ -54,15 +54,17 @@ __device__ __forceinline__ void garner_digits(uint32_t (&X)[E][(NM + 3) / 4]) {
             for (int e = 0; e < E; e++) acc[e] = dp4a_ss(X[e][g], cw, acc[e]);
         });
         constexpr uint32_t sel = l % 4 == 0 ? 0x3214u : l % 4 == 1 ? 0x3240u : l % 4 == 2 ? 0x3410u : 0x4210u;
-#pragma unroll
-        for (int e = 0; e < E; e++) {
+        uint32_t xl[E];                                                                  // balanced digits, low bytes
 #ifndef OZ_INT_REDUCE
-            const uint32_t xl = balanced_float<l>(acc[e]);                               // balanced digit, low byte
+        static_assert(E % 2 == 0, "the elements are reduced in pairs");
+#pragma unroll
+        for (int e = 0; e < E; e += 2) balanced_float_x2<l>(acc[e], acc[e + 1], xl[e], xl[e + 1]);
 #else
-            const uint32_t xl = balanced_magic<l>((uint32_t)acc[e]);                     // balanced digit, low byte
+#pragma unroll
+        for (int e = 0; e < E; e++) xl[e] = balanced_magic<l>((uint32_t)acc[e]);
 #endif
-            X[e][l / 4] = __byte_perm(X[e][l / 4], xl, sel);                             // byte l%4 <- xl
-        }
+#pragma unroll
+        for (int e = 0; e < E; e++) X[e][l / 4] = __byte_perm(X[e][l / 4], xl[e], sel);     // byte l%4 <- xl
     });
 }
 

@@ -75,6 +75,23 @@ __device__ __forceinline__ uint32_t balanced_float(int biased) {
     const float q = __fadd_rn(__fmaf_rn(__fadd_rn(A, -C), inv, C), -C);
     return (uint32_t)__float_as_int(__fmaf_rn(q, -m, A));
 }
+// Two sums at once with the packed FP32 instructions of sm_100 (add.f32x2 / fma.rn.f32x2: one instruction, two lanes, each
+// lane rounded like the scalar form -- same bits, half the instruction slots; these kernels are bound by instruction issue).
+template <int L>
+__device__ __forceinline__ void balanced_float_x2(int biased0, int biased1, uint32_t &x0, uint32_t &x1) {
+#ifdef OZ_NO_F32X2
+    x0 = balanced_float<L>(biased0);
+    x1 = balanced_float<L>(biased1);
+#else
+    static_assert(modulus(L) % 2 == 1, "an even modulus has ties");
+    constexpr float C = 12582912.0f, inv = 1.0f / (float)modulus(L), m = (float)modulus(L);
+    const float2 A = make_float2(__int_as_float(biased0), __int_as_float(biased1));
+    const float2 q = __fadd2_rn(__ffma2_rn(__fadd2_rn(A, make_float2(-C, -C)), make_float2(inv, inv), make_float2(C, C)), make_float2(-C, -C));
+    const float2 X = __ffma2_rn(q, make_float2(-m, -m), A);
+    x0 = (uint32_t)__float_as_int(X.x);
+    x1 = (uint32_t)__float_as_int(X.y);
+#endif
+}
 // 2^s as a double for -1022 <= s <= 1023
 __device__ __forceinline__ double pow2_normal(int s) { return __hiloint2double((s + 1023) << 20, 0); }
 // llrint(ldexp(x, s)) as the reference computes it (src/ozaki2.cuh:76). For s in the normal exponent range the scaling

@@ -44,7 +44,8 @@ __device__ __forceinline__ void residues_of_4(const long long (&v)[4], Put &&put
         constexpr int seed = FLOAT_BIAS - pow2_mod(62, m);
         static_assert(BYTES_BOUND + 256 < (1 << 22), "the byte sum must fit the float's mantissa");
 #pragma unroll
-        for (int e = 0; e < 4; e++) x[e] = balanced_float<l>(dp4a_us(hi[e], whi, dp4a_us(lo[e], wlo, seed)));
+        for (int e = 0; e < 4; e += 2)
+            balanced_float_x2<l>(dp4a_us(hi[e], whi, dp4a_us(lo[e], wlo, seed)), dp4a_us(hi[e + 1], whi, dp4a_us(lo[e + 1], wlo, seed)), x[e], x[e + 1]);
 #else
 #pragma unroll
         for (int e = 0; e < 4; e++) x[e] = balanced_magic<l>((uint32_t)dp4a_us(hi[e], whi, dp4a_us(lo[e], wlo, init)));
