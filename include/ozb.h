@@ -173,6 +173,12 @@ int ozb_mg_wait(ozb_mg *g);
  * in ozb_mg_info, *pieces = transfers of B, *ranges = K ranges whose GEMMs are launched as their pieces land (1: one launch
  * after the last piece). Any pointer may be NULL. */
 int ozb_mg_schedule(int m_local, int N, int K, int moduli, int *layout, int *pieces, int *ranges);
+/* The pieces themselves: piece i carries rows [k0[i], k0[i] + len[i]) of B; range_len[i] > 0 says that the GEMMs of the K
+ * range [range_k0[i], range_k0[i] + range_len[i]) are launched behind it. `layout` 0 / 1 as above, -1: as the library would
+ * choose. Fills at most `cap` entries of each array (NULL arrays are skipped) and returns the number of pieces, or a
+ * negative error code (-OZB_EARG, -OZB_EK). Plain arithmetic, no device needed. */
+int ozb_mg_schedule_pieces(int m_local, int N, int K, int moduli, int layout, int cap, int *k0, int *len, int *range_k0,
+                           int *range_len);
 /* How the last device-operand product moved B: *layout 0 = in one transfer, 1 = column maxima first, then pieces of rows
  * consumed as they land; *pieces = number of transfers of B; *kernels = kernels of this library it launched on this rank
  * (NCCL's own are not counted). Any pointer may be NULL. */

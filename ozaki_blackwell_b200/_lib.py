@@ -76,6 +76,7 @@ lib.ozb_mg_dgemm.argtypes = [_p, _i, _i, _i, _p, _ll, _p, _ll, _p, _ll, _i, _i, 
 lib.ozb_mg_wait.argtypes = [_p]
 lib.ozb_mg_info.argtypes = [_p, _ip, _ip, _ip]
 lib.ozb_mg_schedule.argtypes = [_i, _i, _i, _i, _ip, _ip, _ip]
+lib.ozb_mg_schedule_pieces.argtypes = [_i, _i, _i, _i, _i, _i, _ip, _ip, _ip, _ip]
 lib.ozb_status.argtypes = []
 lib.ozb_bounds_report.argtypes = [ctypes.POINTER(ctypes.c_ulonglong * 4)]
 lib.ozb_selftest_bounds.argtypes = []
@@ -87,5 +88,5 @@ SYMBOLS = [
     "ozb_plan_panel", "ozb_plan_b_begin", "ozb_plan_b_rows", "ozb_plan_b_finish", "ozb_plan_multiply", "ozb_cols_absmax", "ozb_plan_b_rows_residues", "ozb_plan_view", "ozb_plan_status", "ozb_plan_profile", "ozb_plan_phase_ms", "ozb_plan_kernel_ms", "ozb_dgemm_ex", "ozb_dgemm_norm", "ozb_scales_norm", "ozb_ddgemm_ex", "ozb_bf16_fp8_gemm",
     "ozb_scale_residues_rows", "ozb_scale_residues_cols", "ozb_scale_residues_cols_static", "ozb_gemm_i8", "ozb_gemm_i8_mod", "ozb_gemm_i8_mod_beside", "ozb_crt_i32", "ozb_crt_i8",
     "ozb_status", "ozb_int8_peak", "ozb_selftest_wait_expiry", "ozb_bounds_report", "ozb_selftest_bounds",
-    "ozb_dgemm_mg", "ozb_mg_release", "ozb_mg_unique_id", "ozb_mg_create", "ozb_mg_destroy", "ozb_mg_dgemm", "ozb_mg_wait", "ozb_mg_info", "ozb_mg_schedule",
+    "ozb_dgemm_mg", "ozb_mg_release", "ozb_mg_unique_id", "ozb_mg_create", "ozb_mg_destroy", "ozb_mg_dgemm", "ozb_mg_wait", "ozb_mg_info", "ozb_mg_schedule", "ozb_mg_schedule_pieces",
 ]

@@ -637,6 +637,24 @@ OZB_API int ozb_mg_schedule(int m_local, int N, int K, int moduli, int *layout, 
     return 0;
 }
 
+OZB_API int ozb_mg_schedule_pieces(int m_local, int N, int K, int moduli, int layout, int cap, int *k0, int *len, int *range_k0,
+                                   int *range_len) {
+    if (m_local <= 0 || N <= 0 || K <= 0 || moduli < 8 || moduli > 16 || layout < -1 || layout > 1 || cap < 0) return -OZB_EARG;
+    if (K >= 131072) return -OZB_EK;
+    const int lay = layout < 0 ? choose_layout(m_local, K, N, moduli) : layout;
+    Piece sched[MG_MAX_PIECES];
+    int np = 1;
+    if (lay == LAYOUT_STREAM) np = stream_schedule(K, N, sched);
+    else sched[0] = Piece{0, K, 0, K};
+    for (int i = 0; i < np && i < cap; i++) {
+        if (k0) k0[i] = sched[i].k0;
+        if (len) len[i] = sched[i].len;
+        if (range_k0) range_k0[i] = sched[i].range_k0;
+        if (range_len) range_len[i] = sched[i].range_len;
+    }
+    return np;
+}
+
 OZB_API int ozb_mg_info(ozb_mg *g, int *layout, int *pieces, int *kernels) {
     if (!g) return OZB_EARG;
     if (layout) *layout = g->last_layout;

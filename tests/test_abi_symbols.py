@@ -90,3 +90,38 @@ def test_cpp_header_compiles_as_plain_cxx(tmp_path):
     src.write_text('#include "ozaki2.hpp"\nint main() { return oz::MAXM == 49 ? 0 : 1; }\n')
     subprocess.run(["g++", "-std=c++17", "-fsyntax-only", "-I", os.path.join(ROOT, "include"), str(src)], check=True)
     subprocess.run(["gcc", "-std=c99", "-fsyntax-only", "-x", "c", os.path.join(ROOT, "include", "ozb.h")], check=True)
+
+
+def test_the_pieces_of_b_tile_k_and_so_do_the_ranges():
+    """ozb_mg_schedule_pieces for many shapes, both layouts: the pieces cover [0, K) in order without gaps, the K ranges
+    cover [0, K) in order without gaps, every range ends where its piece ends, the last piece closes the last range, and
+    there are fewer than 64 pieces (the handle's event arrays)."""
+    import random
+    from ozaki_blackwell_b200._lib import lib
+    rng = random.Random(7)
+    shapes = [(4096, 32768, 32768), (16384, 32768, 32768), (8192, 8192, 8192), (1, 1, 1), (5, 7, 3), (300, 1000, 777), (64, 16, 131071),
+              (8192, 65536, 12289), (8192, 200000, 100000), (128, 131, 12288), (128, 131, 12416)]
+    shapes += [(rng.randint(1, 20000), rng.randint(1, 70000), rng.randint(1, 131071)) for _ in range(300)]
+    arr = lambda: (ctypes.c_int * 64)()
+    for m, n, k in shapes:
+        for layout in (-1, 0, 1):
+            k0, ln, r0, rl = arr(), arr(), arr(), arr()
+            np_ = lib.ozb_mg_schedule_pieces(m, n, k, 16, layout, 64, k0, ln, r0, rl)
+            assert 1 <= np_ < 64, (m, n, k, layout, np_)
+            at = rat = 0
+            for i in range(np_):
+                assert k0[i] == at and ln[i] > 0, (m, n, k, layout, i)
+                at += ln[i]
+                if rl[i] > 0:
+                    assert r0[i] == rat and r0[i] + rl[i] == at, (m, n, k, layout, i)
+                    rat = at
+            assert at == k and rat == k, (m, n, k, layout, at, rat)
+            if layout == 0:
+                assert np_ == 1
+            lay, pcs, rgs = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+            if layout == -1:
+                assert lib.ozb_mg_schedule(m, n, k, 16, ctypes.byref(lay), ctypes.byref(pcs), ctypes.byref(rgs)) == 0
+                assert pcs.value == np_ and rgs.value == sum(1 for i in range(np_) if rl[i] > 0)
+    assert lib.ozb_mg_schedule_pieces(0, 4, 4, 16, -1, 0, None, None, None, None) == -10001
+    assert lib.ozb_mg_schedule_pieces(4, 4, 131072, 16, -1, 0, None, None, None, None) == -10002
+    assert lib.ozb_mg_schedule_pieces(4, 4, 4, 16, 2, 0, None, None, None, None) == -10001
